@@ -525,3 +525,24 @@ def testing_wait_runs_out(limit: int = 10000) -> bool:
     flag = torch.zeros(1, dtype=torch.int32, device="cuda")
     _call(fn, int(limit), _ptr(flag), _stream())
     return bool(flag.item())
+
+
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act(gu: torch.Tensor, act: str, pairs: bool = False) -> torch.Tensor:
+    """act(gate) * up in 32-bit with one rounding.  gu[M, 2*I] (rows may be strided) holds gate in its first I columns
+    and up in the rest, or with ``pairs`` gate_i and up_i side by side.  act: "silu" or "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    _need_cuda(gu, what="gated_act")
+    if act not in GATE_ACTS:
+        raise KernelError(f"gated_act: unknown activation {act!r}; known: {sorted(GATE_ACTS)}")
+    M, two_i = gu.shape
+    if two_i % 2 or gu.stride(1) != 1:
+        raise KernelError("gated_act: expected [M, 2*I] with dense rows")
+    from .lib import declare
+    out = torch.empty((M, two_i // 2), dtype=gu.dtype, device=gu.device)
+    fn = declare("ti_gated_act", [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                  ctypes.c_int, ctypes.c_int, ctypes.c_void_p])
+    _call(fn, _ptr(gu), gu.stride(0), _ptr(out), M, two_i // 2, 1 if pairs else 0, GATE_ACTS[act], _code(gu, "gated_act"), _stream())
+    return out

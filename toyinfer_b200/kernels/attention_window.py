@@ -1,0 +1,124 @@
+"""Sliding-window attention with several score maps per head, softmax or sigmoid weights, and a logarithmic distance
+term (csrc/attn_window.cu)."""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import KernelError, _call, _code, _need_cuda, _ptr, _stream
+from .gemm import sm_count
+from .wide import _fn
+
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+MODES = {"softmax": 0, "sigmoid": 1}
+
+
+def _pages(mem, dtype, n_kv: int, key_width: int, vdim: int, what: str):
+    kp, vp, pt = mem.k_pages, mem.v_pages, mem.page_table
+    if vp is None or mem.ring_rows:
+        raise KernelError(f"{what}: needs keys and values of all positions (no ring, a value array)")
+    if kp.dtype != dtype or vp.dtype != dtype or tuple(kp.shape[1:]) != (n_kv, mem.page_size, key_width) \
+            or tuple(vp.shape[1:]) != (n_kv, mem.page_size, vdim) or not kp.is_contiguous() or not vp.is_contiguous():
+        raise KernelError(f"{what}: the cache pages do not fit {n_kv} kv heads of {key_width} and {vdim} elements in {dtype}")
+    return _ptr(kp), _ptr(vp), _ptr(pt), pt.shape[1], mem.page_size, kp.shape[0]
+
+
+def prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], eps: float,
+            tables, n_heads: int, n_kv: int, maps: int, dim: int, vdim: int, mem, batch) -> None:
+    """qkv [M, >= heads * maps * dim + kv_heads * (maps * dim + vdim)], one projection's rows (further columns are left
+    alone): adds ``bias`` (float32, q, k and v's length), norms all of q's and all of k's elements at once (weights float32
+    of those lengths, or None), rotates the first ``rot`` elements of every map of q and k (``tables`` = (cos, sin, rot)
+    or None), leaves the queries in place and stores keys and values in ``mem``."""
+    _need_cuda(qkv, bias, q_w, k_w, what="attention_window.prepare")
+    M, N = qkv.shape
+    nq, nk, nv = n_heads * maps * dim, n_kv * maps * dim, n_kv * vdim
+    if N < nq + nk + nv or qkv.stride(1) != 1:
+        raise KernelError("attention_window.prepare: the projection's rows do not fit the heads")
+    for t, n in ((bias, nq + nk + nv), (q_w, nq), (k_w, nk)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError("attention_window.prepare: biases and norm weights must be dense float32")
+    cos = sin = None
+    rot = max_pos = 0
+    if tables is not None:
+        cos, sin, rot = tables
+        max_pos = cos.shape[0]
+        if cos.dtype != torch.float32 or cos.shape != sin.shape or cos.shape[1] * 2 != rot or rot > dim or not cos.is_contiguous():
+            raise KernelError("attention_window.prepare: rotary tables must be float32 [positions, rot / 2] with rot <= dim")
+        if batch.max_pos_after > max_pos:
+            raise KernelError(f"attention_window.prepare: position {batch.max_pos_after - 1} is beyond the rotary tables' {max_pos}")
+    _call(_fn("ti_attn_window_prepare", [P, L, P, P, P, F, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P]),
+          _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos), _ptr(sin), int(rot), int(max_pos),
+          _ptr(batch.tok_pos), _ptr(batch.tok_seq), _ptr(batch.seq_slot),
+          *_pages(mem, qkv.dtype, n_kv, maps * dim, vdim, "attention_window.prepare"), M, n_heads, n_kv, maps, dim, vdim,
+          _code(qkv, "attention_window"), _stream())
+
+
+def decode_splits(n_seq: int, n_virtual: int, per_block: int, span: int, sms: int) -> int:
+    """Ranges that a single query's visible keys (``span``: the window, or the planned length when that is shorter) are
+    cut into, so that the step has about four blocks per SM but no range shorter than 128 keys."""
+    want = max(1, (4 * sms) // max(1, n_seq * n_virtual // per_block))
+    return max(1, min(want, (span + 127) // 128, 64))
+
+
+def heads_per_block(n_heads: int, n_kv: int) -> int:
+    group = n_heads // n_kv
+    return 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
+
+
+def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int, mode: str, batch,
+           r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None, pb: Optional[torch.Tensor] = None,
+           out_f32: bool = False) -> torch.Tensor:
+    """q [M, heads * maps, dim] (prepared) over the keys and values that ``mem`` holds, the step's own included ->
+    [M, heads * maps * vdim] (float32 with ``out_f32``, else q's type).  Key j is visible to query i when
+    0 <= i - j < window.  r1, r2: float32 [heads], the score loses r1 ln(1 + r2 (i - j)); pb: float32 [heads], added to
+    the score under the sigmoid.  mode: "softmax" or "sigmoid" (weights not normalised over the keys)."""
+    _need_cuda(q, r1, r2, pb, what="attention_window")
+    M, HV, dim = q.shape
+    if HV % maps or q.stride(2) != 1 or q.stride(1) != dim:
+        raise KernelError("attention_window: heads of a token must be dense")
+    H = HV // maps
+    for t in (r1, r2, pb):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != H or not t.is_contiguous()):
+            raise KernelError("attention_window: per-head constants must be dense float32 [heads]")
+    if mode not in MODES:
+        raise KernelError(f"attention_window: unknown mode {mode!r}")
+    G = mem.n_kv_heads
+    pages = _pages(mem, q.dtype, G, maps * dim, vdim, "attention_window")
+    out = torch.zeros((M, HV * vdim), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+    code = _code(q, "attention_window")
+    if batch.mode == "extend":
+        span = min(batch.plan_len, window) if window > 0 else batch.plan_len
+        splits = decode_splits(M, HV, heads_per_block(H, G), span, sm_count(q.device))
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((M, HV, splits, vdim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((M, HV, splits, 2), dtype=torch.float32, device=q.device)
+        _call(_fn("ti_attn_window_decode", [P, L, P, L, I, P, P, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, F, I, I, I, P, P, I, P]),
+              _ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(batch.seq_len), _ptr(batch.seq_slot), M, *pages,
+              _ptr(r1), _ptr(r2), _ptr(pb), H, G, maps, dim, vdim, float(scale), int(window), MODES[mode], splits, _ptr(part_o),
+              _ptr(part_ml), code, _stream(), launches=2 if splits > 1 else 1)
+        return out
+    _call(_fn("ti_attn_window", [P, L, P, L, I, P, P, P, I, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, F, I, I, I, P]),
+          _ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(batch.cu_new), _ptr(batch.seq_start),
+          _ptr(batch.seq_slot), batch.n_seq, batch.max_new, *pages, _ptr(r1), _ptr(r2), _ptr(pb), H, G, maps, dim, vdim, float(scale),
+          int(window), MODES[mode], code, _stream())
+    return out
+
+
+def diff_combine(a: torch.Tensor, gate: Optional[torch.Tensor], n_heads: int, vdim: int, lam: float, diff: float, eps: float,
+                 out_dtype: torch.dtype) -> torch.Tensor:
+    """a float32 [M, heads * 2 * vdim] (per head the two maps' outputs a1, a2), gate [M, heads] logits of ``out_dtype`` (rows
+    may be strided) or None -> (a1 - lam a2) / rms(.) * (1 - diff) * sigmoid(gate), [M, heads * vdim] in ``out_dtype``."""
+    _need_cuda(a, gate, what="diff_combine")
+    M = a.shape[0]
+    if a.dtype != torch.float32 or tuple(a.shape) != (M, n_heads * 2 * vdim) or not a.is_contiguous():
+        raise KernelError("diff_combine: the maps' outputs must be dense float32 [tokens, heads * 2 * vdim]")
+    if gate is not None and (tuple(gate.shape) != (M, n_heads) or gate.dtype != out_dtype or gate.stride(1) != 1):
+        raise KernelError("diff_combine: the gate must be [tokens, heads] of the output's type")
+    out = torch.empty((M, n_heads * vdim), dtype=out_dtype, device=a.device)
+    _call(_fn("ti_diff_combine", [P, P, L, P, L, I, I, I, F, F, F, I, P]), _ptr(a), _ptr(gate), gate.stride(0) if gate is not None else 0,
+          _ptr(out), out.stride(0), M, int(n_heads), int(vdim), float(lam), float(diff), float(eps),
+          0 if out_dtype == torch.float32 else 1, _stream())
+    return out

@@ -150,3 +150,42 @@ def block_diag_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         xb, wb, ob = x[:, b * Kb:(b + 1) * Kb], w[b], out[:, b * N:(b + 1) * N]
         gemm.run(xb, wb, ob, M, N, Kb, xb.stride(0), wb.stride(0))
     return out
+
+
+def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, rate: torch.Tensor, skip: Optional[torch.Tensor],
+             n_heads: int, groups: int, n_state: int, vdim: int, state: torch.Tensor, state_offset: int, batch) -> torch.Tensor:
+    """The Mamba-2 recurrence over every sequence's new tokens (csrc/ssd_scan.cu).  xbc [M, heads * vdim + 2 * groups *
+    n_state]: x, B and C after their convolution and silu; dt_raw [M, heads] the raw step sizes (rows may be strided);
+    dt_bias, rate (= exp(A_log)) and skip float32 [heads].  Returns float32 y [M, heads * vdim]; the state
+    [heads, vdim, n_state] per slot is left as it is after the step's tokens."""
+    _need_cuda(xbc, dt_raw, dt_bias, rate, skip, state, what="ssd_scan")
+    M = xbc.shape[0]
+    inner = n_heads * vdim
+    if xbc.dim() != 2 or xbc.shape[1] != inner + 2 * groups * n_state or xbc.stride(1) != 1:
+        raise KernelError("ssd_scan: x, B and C do not fit the heads, groups and state")
+    if tuple(dt_raw.shape) != (M, n_heads) or dt_raw.dtype != xbc.dtype or dt_raw.stride(1) != 1:
+        raise KernelError("ssd_scan: the step sizes must be [tokens, heads] of the tokens' type")
+    for t, what in ((dt_bias, "step-size bias"), (rate, "rate"), (skip, "skip weight")):
+        _vec(t, n_heads, f"ssd_scan: the {what}")
+    base, stride = _state_part(state, state_offset, inner * n_state, "ssd_scan")
+    y = torch.zeros((M, inner), dtype=torch.float32, device=xbc.device)         # rows that are nobody's stay zero
+    _call(_fn("ti_ssd_scan", [P, L, P, L, P, P, P, P, L, P, P, P, I, I, I, I, I, I, P]),
+          _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(rate), _ptr(skip), base, stride, _ptr(y),
+          _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, int(n_heads), int(groups), int(n_state), int(vdim),
+          _code(xbc, "ssd_scan"), _stream())
+    return y
+
+
+def gate_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """y float32 [M, inner], z [M, inner] gate logits of the engine's type (rows may be strided), w float32 [inner] ->
+    u / rms(u) * w with u = y * silu(z) and the root mean square taken over each of ``groups`` equal parts of the row, in
+    the gate's type.  The gate comes before the norm."""
+    _need_cuda(y, z, w, what="gate_group_rmsnorm")
+    M, N = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or tuple(z.shape) != (M, N) or z.stride(1) != 1 or groups < 1 or N % groups:
+        raise KernelError("gate_group_rmsnorm: y must be dense float32, the gate of its shape, the parts equal")
+    _vec(w, N, "gate_group_rmsnorm: the weight")
+    out = torch.empty((M, N), dtype=z.dtype, device=y.device)
+    _call(_fn("ti_gate_group_rmsnorm", [P, P, L, P, P, I, I, I, F, I, P]), _ptr(y), _ptr(z), z.stride(0), _ptr(w), _ptr(out), M, N,
+          int(groups), float(eps), _code(z, "gate_group_rmsnorm"), _stream())
+    return out

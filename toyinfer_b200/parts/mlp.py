@@ -55,6 +55,38 @@ class SwiGLU(FeedForward):
 register_part("feed_forward", "swiglu", SwiGLU)
 
 
+class GatedDense(FeedForward):
+    """y = Wdown (act(Wgate x) * (Wup x)) with ``act`` "gelu_tanh" or "silu"; no bias.  Gate and up rows are one matrix
+    (gate's rows, then up's), so one product makes both; the activation and the product of the two halves run in 32-bit
+    with one rounding (kernels.gated_act).  With "silu" this is the SwiGLU above without its paired rows."""
+
+    captures_start = True
+
+    def __init__(self, ctx: BuildContext, prefix: str, intermediate_size: int, act: str = "gelu_tanh",
+                 names: Optional[Dict[str, str]] = None):
+        self.hidden = ctx.hidden_size
+        self.inter = int(intermediate_size)
+        if act not in K.GATE_ACTS:
+            raise ValueError(f"feed-forward at {prefix!r}: unknown activation {act!r}; known: {sorted(K.GATE_ACTS)}")
+        self.act = act
+        n = {"gate": "gate", "up": "up", "down": "down"}
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.w_gate_up = self.w_down = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.names["gate"]: ParamSpec((self.inter, self.hidden), std=0.05),
+                self.names["up"]: ParamSpec((self.inter, self.hidden), std=0.05),
+                self.names["down"]: ParamSpec((self.hidden, self.inter), std=0.05)}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_gate_up = torch.cat([tensors.pop(self.names["gate"]), tensors.pop(self.names["up"])], dim=0).contiguous()
+        self.w_down = tensors.pop(self.names["down"]).contiguous()
+
+    def forward(self, x, batch) -> torch.Tensor:
+        return K.linear(K.gated_act(K.linear(x, self.w_gate_up), self.act), self.w_down)
+
+
 class SquaredReLU(FeedForward):
     """y = Wdown relu(Wup x)^2; no gate, no bias."""
 
@@ -131,6 +163,7 @@ class TableMoE(FeedForward):
         return KM.experts_ffn(x, perm, off, self.w_gate_up, self.w_down, self.top, self.limit, self.alpha, 1.0 / self.top)
 
 
+register_part("feed_forward", "gated_dense", GatedDense)
 register_part("feed_forward", "relu2", SquaredReLU)
 register_part("feed_forward", "table_moe", TableMoE)
 

@@ -104,3 +104,45 @@ class StreamRMSNorm(Norm):
 
 
 register_part("norm", "stream_rmsnorm", StreamRMSNorm)
+
+
+class WideScalarRMSNorm(Norm):
+    """RMS norm over a float32 residual stream whose weight is ONE number (``scalar``) or one per channel, in a design
+    that norms a sublayer's output as well as its input: what is pending on the stream is a sublayer's output that still
+    has to pass a norm of this kind (``pending(y)`` makes it, kernels.wide.PostNormed), and the next norm that reads the
+    stream forms rmsnorm(y) * w_post, adds it in 32-bit and norms the sum, in one kernel.  The weight is float32 whatever
+    the engine's type; the normed rows come out in the engine's type."""
+
+    def __init__(self, ctx: BuildContext, prefix: str, size: int, eps: float, name: str = "weight", scalar: bool = True):
+        self.size, self.eps, self.scalar = int(size), float(eps), bool(scalar)
+        self.weight_name = prefix + name
+        self.weight: Optional[torch.Tensor] = None
+        self.out_dtype = ctx.dtype
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec(() if self.scalar else (self.size,), role="norm", init="one_plus_normal", std=0.1)}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].to(torch.float32).reshape(-1).contiguous()
+
+    def pending(self, y: torch.Tensor) -> "wide.PostNormed":
+        """y as something that passes this norm before it is added to the stream."""
+        return wide.PostNormed(y, self.weight, self.eps)
+
+    def _check(self, delta) -> None:
+        if delta is not None and not isinstance(delta, wide.PostNormed):
+            raise ValueError("a stream with normed sublayer outputs takes what a norm's pending() made, nothing else")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return wide.post_norm_add_norm(x, None, self.weight, self.eps, self.out_dtype)
+
+    def add_forward(self, h: torch.Tensor, delta) -> torch.Tensor:
+        self._check(delta)
+        return wide.post_norm_add_norm(h, delta, self.weight, self.eps, self.out_dtype)
+
+    def gather_add_forward(self, h: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        self._check(delta)
+        return wide.post_norm_add_norm(h, delta, self.weight, self.eps, self.out_dtype, rows=rows)
+
+
+register_part("norm", "wide_scalar_rmsnorm", WideScalarRMSNorm)

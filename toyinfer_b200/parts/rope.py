@@ -38,11 +38,28 @@ def blended_frequencies(dim: int, theta: float, factor: float, original: int, fa
     return base / factor * ramp + base * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+def banded_frequencies(dim: int, theta: float, factor: float, original: int, low: float, high: float):
+    """Frequencies rescaled by wavelength bands, as Llama 3.1 stretches its context: with wavelength l = 2 pi / f, a pair
+    keeps f where l < original / high, gets f / factor where l > original / low, and between the two, with
+    s = (original / l - low) / (high - low), (1 - s) f / factor + s f.  Returns float64 frequencies (no magnitude)."""
+    half = dim // 2
+    i = torch.arange(half, dtype=torch.float64)
+    base = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -(2.0 * i) / dim)
+    wavelength = 2.0 * math.pi / base
+    s = (original / wavelength - low) / (high - low) if high != low else torch.ones_like(base)
+    mid = (1.0 - s) * base / factor + s * base
+    return torch.where(wavelength < original / high, base, torch.where(wavelength > original / low, base / factor, mid))
+
+
 def rotary_tables(dim: int, theta: float, max_positions: int, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """cos and sin of pos * f_i with f_i = theta^(-2i/dim) (or the blended frequencies and magnitude of ``scaling``:
-    factor, original, fast, slow), computed in 64-bit, returned as float32."""
+    factor, original, fast, slow; or, with ``kind`` "bands", the banded frequencies of factor, original, low, high),
+    computed in 64-bit, returned as float32."""
     half = dim // 2
-    if scaling:
+    if scaling and scaling.get("kind") == "bands":
+        inv_freq, magnitude = banded_frequencies(dim, float(theta), float(scaling["factor"]), int(scaling["original"]),
+                                                 float(scaling["low"]), float(scaling["high"])), 1.0
+    elif scaling:
         inv_freq, magnitude = blended_frequencies(dim, float(theta), float(scaling["factor"]), int(scaling["original"]),
                                                   float(scaling["fast"]), float(scaling["slow"]))
     else:
@@ -54,7 +71,8 @@ def rotary_tables(dim: int, theta: float, max_positions: int, scaling: Optional[
 
 
 class RotaryHalf(PositionEncoding):
-    """``scaling``: None, or the stretch for long contexts (see blended_frequencies).  ``max_positions`` is the
+    """``scaling``: None, or the stretch for long contexts (see blended_frequencies; with ``kind`` "bands" see
+    banded_frequencies).  ``max_positions`` is the
     most the tables may ever hold; with ``lazy`` they are built for as many positions as ``ensure`` is told (the
     engine says how long its sequences get before the first step), not for the model's nominal limit."""
 
@@ -67,11 +85,12 @@ class RotaryHalf(PositionEncoding):
         self.max_positions = int(max_positions)
         self.scaling = dict(scaling) if scaling else None
         if self.scaling:
-            for key in ("factor", "original", "fast", "slow"):
+            bands = self.scaling.get("kind") == "bands"
+            keys = ("factor", "original", "low", "high") if bands else ("factor", "original", "fast", "slow")
+            for key in keys:
                 if key not in self.scaling:
                     raise ValueError(f"rotary scaling needs {key!r}")
-            if not (self.scaling["factor"] >= 1.0 and self.scaling["original"] > 0
-                    and self.scaling["fast"] > 0 and self.scaling["slow"] > 0):
+            if not all(self.scaling[key] > 0 for key in keys) or (not bands and self.scaling["factor"] < 1.0):
                 raise ValueError(f"rotary scaling out of range: {self.scaling}")
         self.device = ctx.device
         self.cos = self.sin = None
