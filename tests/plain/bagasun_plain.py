@@ -84,14 +84,20 @@ def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor) -> torc
     return out
 
 
+def visible(m: dict, T: int) -> int:
+    """How many positions a query sees, itself included: mask.size, or all when there is no mask."""
+    return int(m["mask"]["size"]) if m.get("mask") else T
+
+
 def sigmoid_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: float) -> torch.Tensor:
     """h [T, width]; p: the mixer's tensors by their short names (q, q.b, k, ..., q.norm, k.norm, r1, r2, pb, o)."""
     T = h.shape[0]
     H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    window, scale = m["mask"]["size"], float(m["scale"])
-    q = unit_rms(h @ p["q"].T + p["q.b"], eps) * p["q.norm"]
-    k = unit_rms(h @ p["k"].T + p["k.b"], eps) * p["k.norm"]
-    v = h @ p["v"].T + p["v.b"]
+    window, scale = visible(m, T), float(m["scale"])
+    zero = torch.zeros((), dtype=F64)
+    q, k, v = (h @ p[n].T + p.get(n + ".b", zero) for n in ("q", "k", "v"))        # biases, the norm, the distance term and
+    if "q.norm" in p:                                                              # the head's bias are each optional
+        q, k = unit_rms(q, eps) * p["q.norm"], unit_rms(k, eps) * p["k.norm"]
     q, k, v = q.view(T, H, d), k.view(T, G, d), v.view(T, G, vd)
     out = torch.zeros(T, H, vd, dtype=F64)
     for hd in range(H):
@@ -99,8 +105,10 @@ def sigmoid_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps:
         for i in range(T):
             lo = max(0, i - window + 1)
             dist = torch.arange(i - lo, -1, -1, dtype=F64)                      # i - j for j = lo .. i
-            s = (k[lo:i + 1, g] @ q[i, hd]) * scale - p["r1"][hd] * torch.log(1.0 + p["r2"][hd] * dist)
-            out[i, hd] = sigmoid(s + p["pb"][hd]) @ v[lo:i + 1, g]
+            s = (k[lo:i + 1, g] @ q[i, hd]) * scale
+            if "r1" in p:
+                s = s - p["r1"][hd] * torch.log(1.0 + p["r2"][hd] * dist)
+            out[i, hd] = sigmoid(s + (p["pb"][hd] if "pb" in p else 0.0)) @ v[lo:i + 1, g]
     return out.reshape(T, H * vd) @ p["o"].T
 
 
@@ -135,7 +143,7 @@ def rotate_maps(x: torch.Tensor, dims: int, freqs: torch.Tensor, first_position:
 def diff_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    window, scale, diff = m["mask"]["size"], float(m["scale"]), float(m["diff"])
+    window, scale, diff = visible(m, T), float(m["scale"]), float(m["diff"])
     q = (h @ p["q"].T).view(T, H * 2, d)
     k = (h @ p["k"].T).view(T, G * 2, d)
     v = (h @ p["v"].T).view(T, G, vd)
@@ -145,7 +153,7 @@ def diff_attention(h: torch.Tensor, p: Dict[str, torch.Tensor], m: dict, eps: fl
         q, k = rotate_maps(q, rot["dims"], f), rotate_maps(k, rot["dims"], f)
     q, k = q.view(T, H, 2, d), k.view(T, G, 2, d)
     lam = math.exp(float((p["lq1"] * p["lk1"]).sum())) - math.exp(float((p["lq2"] * p["lk2"]).sum())) + diff
-    gate = sigmoid(h @ p["g"].T)                                                     # [T, H]
+    gate = sigmoid(h @ p["g"].T) if "g" in p else torch.ones(T, H, dtype=F64)        # [T, H]; the gate is optional
     out = torch.zeros(T, H, vd, dtype=F64)
     for hd in range(H):
         g = hd // (H // G)
@@ -197,10 +205,12 @@ def layer_tensors(weights: Dict[str, torch.Tensor], layer: int, part: str) -> Di
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int]) -> Tuple[torch.Tensor, List[torch.Tensor]]:
     """Returns (logits [T, vocab], the residual stream after every layer run)."""
     eps = float(cfg["norm"]["eps"])
-    x = weights["embed"].to(F64)[list(tokens)] * float(cfg["embedding"]["scale"])
+    x = weights["embed"].to(F64)[list(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     after = []
     for i, L in enumerate(cfg["layers"]):
-        src = L.get("weights_of", i)
+        src = i
+        while cfg["layers"][src].get("weights_of") is not None:          # a shared layer may name another shared one
+            src = cfg["layers"][src]["weights_of"]
         g = lambda name: float(weights[f"l{src}.{name}"])
         mix = MIXERS[L["type"]](scalar_norm(x, g("norm1"), eps), layer_tensors(weights, src, "mix"), L["mixer"], eps)
         x = x + scalar_norm(mix, g("norm1b"), eps)
