@@ -18,7 +18,7 @@ error of the logits of a 512-token prompt's last place and of 8 decoded places.
 Every decode step reads all weights (8 GB) and the live sequences' cache, far more than
 the 126 MB L2, so nothing is flushed between steps.
 
-``--design kadodra`` (or ``tusasun``) measures another design instead (see run_design): prompt and decode rates and
+``--design kadodra`` (or ``tusasun``, ``bagasun``) measures another design instead (see run_design): prompt and decode rates and
 the device time of every stage of a layer at real layer sizes, beside the dense model at equal size.
 """
 from __future__ import annotations
@@ -488,6 +488,27 @@ def _tusasun_config(width, heads, layers, kind, vocab=32000):
             "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
 
 
+def _bagasun_config(width, heads, layers, kind, vocab=32000):
+    """``layers`` equal layers of one kind of mixer over a float32 stream with a norm on either side of every sublayer and a
+    gelu-gated dense feed-forward of 8/3 width: "sigmoid" (sliding-window attention with sigmoid weights and a logarithmic
+    distance term, heads of 128, 4 query heads per kv head), "diff" (differential attention: two maps of 64 per head, values
+    of 128, rotary positions) or "mamba2" (inner width twice the model's in heads of 64, a state of 128, 8 groups)."""
+    window = 1024
+    if kind == "sigmoid":
+        layer = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                                "scale": 128 ** -0.5, "mask": {"size": window}}}
+    elif kind == "diff":
+        layer = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 128, "scale": 64 ** -0.5,
+                                                  "diff": 0.4, "mask": {"size": window},
+                                                  "rot": {"base": 5e5, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0,
+                                                                                                "original": 2048}}}}
+    else:
+        layer = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    layer["mlp"] = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128}
+    return {"architecture": "Bagasun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
+
+
 def _qwen3_like(width, heads, layers, vocab=32000):
     """The dense model of the same width, head count and layers; its three feed-forward matrices of 8/3 width hold what the
     other design's two of 4 width (or its two active experts of three matrices each, 6 width... the nearest round size) hold."""
@@ -504,14 +525,21 @@ def run_design(name: str, widths, layers: int, tokens: int, batch: int, context:
     import torch
     from toyinfer_b200.engine import Engine
     from toyinfer_b200.tracing import Tracer
-    if name not in ("kadodra", "tusasun"):
-        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra, tusasun)")
+    if name not in ("kadodra", "tusasun", "bagasun"):
+        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra, tusasun, bagasun)")
     for width in widths:
         heads = width // 128
         if name == "kadodra":
             models = [("kadodra latent+dense", _kadodra_config(width, heads, layers, "latent")),
                       ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
                       ("qwen3 dense", _qwen3_like(width, heads, layers))]
+        elif name == "bagasun":     # dense feed-forwards: the dense model is its closest relation; the decayed state is lightning's
+            models = [("bagasun sigmoid+dense", _bagasun_config(width, heads, layers, "sigmoid")),
+                      ("bagasun diff+dense", _bagasun_config(width, heads, layers, "diff")),
+                      ("bagasun mamba2+dense", _bagasun_config(width, heads, layers, "mamba2")),
+                      ("qwen3 dense", _qwen3_like(width, heads, layers)),
+                      ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
+                      ("tusasun attention+experts", _tusasun_config(width, heads, layers, "attention"))]
         else:       # its closest relation is the other design with a float32 stream, a state per sequence and experts
             models = [("tusasun attention+experts", _tusasun_config(width, heads, layers, "attention")),
                       ("tusasun rglru+experts", _tusasun_config(width, heads, layers, "rglru")),
@@ -670,6 +698,47 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(1, new, dev), "mixed", [0], [cached], [[0] * new], 1, cached + new)
             return (lambda: K.attention_chunk(q, k, v, mem, 1 / math.sqrt(hd), 0, batch)), \
                 qkv.numel() * 2 + new * nh * hd * 2 + 2 * cached * nkv * hd * 2, 4.0 * nh * hd * new * (cached + (new + 1) / 2)
+        if name.startswith("attn_window"):                # attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]]: a whole prompt
+            from toyinfer_b200.kernels import attention_window as KW
+            opts = name.split(":")[1].split(",") if ":" in name else []
+            T = int(opts[0]) if opts else PREFILL_TOKENS
+            kind = opts[1] if len(opts) > 1 else "sigmoid"
+            window = int(opts[2]) if len(opts) > 2 else 1024
+            KW.tensor_cores = not (len(opts) > 3 and opts[3] == "cuda")
+            nh, nkv = 16, 4
+            maps, hd, vd = (1, 128, 128) if kind == "sigmoid" else (2, 64, 128)
+            pages = (T + 63) // 64
+            table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
+            table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
+            mem = KVView(rnd(pages + 1, nkv, 64, maps * hd), rnd(pages + 1, nkv, 64, vd), table, nkv, maps * hd, 0, 0)
+            nq, nk, nv = nh * maps * hd, nkv * maps * hd, nkv * vd
+            qkv = rnd(T, nq + nk + nv)
+            batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
+            f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
+            r1, r2, pb = (f32(nh), f32(nh), -2 * f32(nh)) if kind == "sigmoid" else (None, None, None)
+            tab = KW.distance_table(r1, r2, pb, nh, window, dev) if kind == "sigmoid" else None
+            KW.prepare(qkv, None, None, None, 1e-6, None, nh, nkv, maps, hd, vd, mem, batch)       # the keys and values into the pages
+            pairs = sum(min(i + 1, window) for i in range(T))
+            return (lambda: KW.attend(qkv[:, :nq].view(T, nh * maps, hd), maps, vd, mem, hd ** -0.5, window,
+                                      "sigmoid" if kind == "sigmoid" else "softmax", batch, r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid",
+                                      k=qkv[:, nq:nq + nk], v=qkv[:, nq + nk:], table=tab)), \
+                qkv.numel() * 2 + T * nh * maps * vd * (2 if kind == "sigmoid" else 4), 2.0 * nh * maps * (hd + vd) * pairs
+        if name.startswith("ssd_scan"):                   # ssd_scan[:TOKENS[,SEGMENT]]: the Mamba-2 recurrence over one prompt
+            from toyinfer_b200.kernels import recurrent as KR
+            opts = name.split(":")[1].split(",") if ":" in name else []
+            T = int(opts[0]) if opts else PREFILL_TOKENS
+            if len(opts) > 1:
+                KR.SSD_SEGMENT = int(opts[1])
+            heads, vd, N, groups = 64, 64, 128, 8
+            inner = heads * vd
+            xbc, dt = rnd(T, inner + 2 * groups * N), rnd(T, heads)
+            f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
+            dt_bias, rate, skip = f32(heads) - 1.0, f32(heads) + 0.5, f32(heads)
+            state = torch.zeros(2, inner * N, dtype=torch.float32, device=dev)
+            batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
+            # x, B, C and the step sizes read, y written in float32; 2 multiply-adds per state element and token
+            return (lambda: KR.ssd_scan(xbc, dt, dt_bias, rate, skip, heads, groups, N, vd, state, 0, batch)), \
+                xbc.numel() * 2 + dt.numel() * 2 + T * inner * 4, 4.0 * T * inner * N
         raise SystemExit(f"unknown kernel case {name!r}")
 
     fn, nbytes, flops = make()
@@ -721,13 +790,14 @@ def main() -> int:
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K[,BN,SPLITS], attn_decode, attn_decode_b64, attn_decode_b1, "
-                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], mma_issue; "
+                    "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], "
+                    "attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]], ssd_scan[:TOKENS[,SEGMENT]], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
     ap.add_argument("--prompt-steps", default="", help="time one prompt step of each of these lengths instead (comma-separated), "
                     "with --layers layers")
-    ap.add_argument("--design", default="", help="measure another design beside its closest relations at equal size instead: kadodra or tusasun "
+    ap.add_argument("--design", default="", help="measure another design beside its closest relations at equal size instead: kadodra, tusasun or bagasun "
                     "(with --widths, --layers, --tokens, --batch, --context)")
     ap.add_argument("--widths", default="2048,4096", help="with --design: model widths (heads of 128)")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="with --design: the prompt's tokens")

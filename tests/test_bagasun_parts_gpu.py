@@ -89,6 +89,10 @@ SIGMOID = [
     dict(n_heads=3, n_kv_heads=3, dim=40, vdim=200, window=130),
     dict(n_heads=8, n_kv_heads=2, dim=64, vdim=64, window=0),                # every earlier key
     dict(n_heads=2, n_kv_heads=2, dim=12, vdim=36, window=1000),             # longer than any sequence here
+    # sizes that the tensor-core kernel takes in bfloat16: windows inside a tile, of three pages and a bit, of one key
+    dict(n_heads=4, n_kv_heads=2, dim=64, vdim=128, window=200),
+    dict(n_heads=2, n_kv_heads=1, dim=128, vdim=128, window=31),
+    dict(n_heads=3, n_kv_heads=3, dim=64, vdim=64, window=1),
 ]
 
 
@@ -143,6 +147,8 @@ DIFF = [
          scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 256}),
     dict(n_heads=4, n_kv_heads=1, dim=128, vdim=64, window=0, rot=64, scaling=None, diff=0.1),
     dict(n_heads=1, n_kv_heads=1, dim=16, vdim=8, window=1, rot=4, scaling=None, diff=0.6),
+    dict(n_heads=2, n_kv_heads=2, dim=64, vdim=64, window=129, rot=64, scaling=None, diff=0.4),
+    dict(n_heads=6, n_kv_heads=2, dim=128, vdim=128, window=200, rot=16, scaling=None, diff=0.7),
 ]
 
 
@@ -183,6 +189,38 @@ def test_differential_attention_every_way_of_feeding(dtype, c):
     xs = [loud_inputs(n, 56, 15 + i, [j for j in (0, 2, 63, 64, 127, 128, 250) if j < n], factor).to(dtype) for i, n in enumerate(lens)]
     wants = [plain.diff_attention(x.double(), w, mcfg, 1e-5) for x in xs]
     check_all_schedules(m, xs, wants, dtype, scale=3.0)
+
+
+@pytest.mark.parametrize("kind,c", [("sigmoid", SIGMOID[3]), ("sigmoid", SIGMOID[7]), ("sigmoid", SIGMOID[8]), ("sigmoid", SIGMOID[9]),
+                                    ("diff", DIFF[3]), ("diff", DIFF[4]), ("diff", DIFF[6]), ("diff", DIFF[7])])
+def test_tensor_core_prompts_and_pieces_agree_with_the_cuda_core_kernel(kind, c, monkeypatch):
+    """bfloat16, keys and values of 64 or 128 elements: the same mixer through the tcgen05 kernel and through the CUDA-core
+    kernel, on whole prompts and on pieces that begin in the middle of a page.  The two differ by the rounding of the
+    weights to bfloat16 for the second product, and a masked key must not leak: a loud row stands just outside a window."""
+    from toyinfer_b200.kernels import attention_window as KW
+    from test_tusasun_parts_gpu import schedules
+    dtype = torch.bfloat16
+    m, w, mcfg = (make_sigmoid if kind == "sigmoid" else make_diff)(dtype, c)
+    calls = []
+    real = KW._fn
+
+    def spy(name, sig):
+        calls.append(name)
+        return real(name, sig)
+    monkeypatch.setattr(KW, "_fn", spy)
+    lens = [333, 130, 64, 2]
+    xs = [loud_inputs(n, 56, 40 + i, [j for j in (1, 63, 64, 140, 330) if j < n], 6.0).to(dtype) for i, n in enumerate(lens)]
+    sch = schedules(lens)
+    got = {name: feed(m, m.memory_request(), xs, s, dtype) for name, s in sch.items()}
+    assert "ti_attn_window_tc" in calls and "ti_attn_window" not in calls
+    monkeypatch.setattr(KW, "tensor_cores", False)
+    calls.clear()
+    for name, s in sch.items():
+        want = feed(m, m.memory_request(), xs, s, dtype)
+        for i, (g, x) in enumerate(zip(got[name], want)):
+            # (the mixer's output is a sum over hundreds of bfloat16 values of size ten: a few hundredths either way)
+            torch.testing.assert_close(g, x, rtol=3e-2, atol=0.15, msg=lambda e: f"{kind} {name}, sequence {i}: {e}")
+    assert "ti_attn_window_tc" not in calls
 
 
 @pytest.mark.parametrize("dtype", DT)
@@ -226,6 +264,37 @@ def test_mamba2_every_way_of_feeding(dtype, c):
     xs = inputs([300, 129, 3], 56, 5, dtype)
     wants = [plain.mamba2(x.double(), w, mcfg, 1e-5) for x in xs]
     check_all_schedules(m, xs, wants, dtype)
+
+
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("c,segment", [(SSM[0], 16), (SSM[1], 16), (SSM[2], 32), (SSM[4], 48), (SSM[2], None)])
+def test_mamba2_segments_in_parallel(dtype, c, segment, monkeypatch):
+    """Long runs of new tokens are cut into segments that run side by side: with short segments every schedule of the
+    other test uses them (sequences of 300, 129 and 3 tokens in one step: eighteen, eight and one segment; pieces that end
+    inside a segment; a state that the prompt before left), and with the real segment length a prompt of 1,000 tokens
+    beside one of 513 and one of 512."""
+    from toyinfer_b200.kernels import recurrent as KR
+    m, w, mcfg = make_ssm(dtype, c)
+    if segment is not None:
+        monkeypatch.setattr(KR, "SSD_SEGMENT", segment)
+        lens = [300, 129, 3]
+    else:
+        lens = [1000, 513, 512]
+    xs = inputs(lens, 56, 31, dtype)
+    wants = [plain.mamba2(x.double(), w, mcfg, 1e-5) for x in xs]
+    if segment is not None:
+        check_all_schedules(m, xs, wants, dtype, scale=3.0)
+        return
+    for sched in ([[(0, 1000), (1, 513), (2, 512)]], [[(0, 40), (1, 1)], [(0, 960), (1, 512), (2, 512)]]):
+        got = feed(m, m.memory_request(), xs, sched, dtype, n_slots=3, pre_use=False)
+        if dtype == torch.bfloat16:
+            # Rounded inputs under decays near one leave a row now and then a tenth away from the exact result, with or
+            # without segments; what segments may change is the order of float32 sums, a rounding step of the output.
+            monkeypatch.setattr(KR, "SSD_SEGMENT", 10 ** 9)
+            wants = feed(m, m.memory_request(), xs, sched, dtype, n_slots=3, pre_use=False)
+            monkeypatch.undo()
+        for g, x in zip(got, wants):
+            torch.testing.assert_close(g, x, **(tol(dtype, 8.0) if dtype == torch.float32 else dict(rtol=2e-2, atol=0.03)))
 
 
 @pytest.mark.parametrize("dtype", DT)

@@ -35,11 +35,16 @@
 // loss); the final division by the running sum makes the result the same.
 // V is stored [position][d]: for the second product that is the "MN-major" form of the B
 // operand, described as such to the MMA instead of being transposed.
+// Keys and values may differ in size (64 or 128 elements each), a head may carry several score
+// maps over one value (differential attention), and the weights may be sigmoids of the scores
+// instead of a softmax (ti_attn_window_tc): the tiles, the two products and the hand-over between
+// the warps are the same, only what the softmax warps do to a score differs.
 #include "tcgen05.cuh"
 
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
 
 namespace {
 constexpr int BQ = 128, BKV = 64, THREADS = 320;      // TMA warp, MMA warp, eight softmax warps
@@ -53,6 +58,11 @@ struct Args {
     // A soft cap on the scaled scores, cap * tanh(s / cap) (cap > 0), and after it a bias by distance:
     // dist_bias[h][min(i - j, far)] is added to the score of query i and key j (float32 [heads, far + 1]; or null).
     float cap; const float* dist_bias; int far;
+    // Score maps per head (differential attention has two): the projection's row holds `maps` queries of a head side by
+    // side and `maps` keys of a kv head side by side, which share the kv head's one value.  A block works on one
+    // (head, map); n_heads and n_kv_heads count real heads.  The output's row holds heads * maps results; with out_f32
+    // they are stored as floats.
+    int maps; int out_f32;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -89,28 +99,30 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 // Shared memory of a block (all dynamic, so that two blocks fit an SM): the query tile, two
 // stages of (K tile, V tile), then the mbarriers.
-template <int HD> struct Smem {
-    static constexpr int Q_BYTES = BQ * HD * 2, KV_BYTES = BKV * HD * 2;
-    static constexpr int Q_OFF = 0, KV_OFF = Q_BYTES, BAR_OFF = KV_OFF + 4 * KV_BYTES;
+template <int HDK, int HDV> struct Smem {
+    static constexpr int Q_BYTES = BQ * HDK * 2, K_BYTES = BKV * HDK * 2, V_BYTES = BKV * HDV * 2, STAGE = K_BYTES + V_BYTES;
+    static constexpr int Q_OFF = 0, KV_OFF = Q_BYTES, BAR_OFF = KV_OFF + 2 * STAGE;
     static constexpr int MX_OFF = BAR_OFF + 256;          // row maxima of the two column halves, two tiles deep
     static constexpr int L_OFF = MX_OFF + 2 * 2 * BQ * 4;  // row sums of the two column halves
     static constexpr int TOTAL = L_OFF + 2 * BQ * 4;
 };
 
-template <int HD, bool PAGED>
+// HDK: elements of a query and a key; HDV: of a value.  MODE 0: softmax over the visible keys.  MODE 1: the weight of
+// a visible key is sigmoid(score * scale + dist_bias[h][i - j]), not normalised over the keys (no maxima, no sums).
+template <int HDK, int HDV, bool PAGED, int MODE>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                        const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap kp_map,
                        const __grid_constant__ CUtensorMap vp_map, Args a, int* status) {
     ti_pdl_trigger();
-    using L = Smem<HD>;
-    constexpr int Q_BYTES = L::Q_BYTES, KV_BYTES = L::KV_BYTES;
+    using L = Smem<HDK, HDV>;
+    constexpr int Q_BYTES = L::Q_BYTES, K_BYTES = L::K_BYTES, V_BYTES = L::V_BYTES, STAGE = L::STAGE;
     constexpr int QBOX = 128 * 128, KBOX = BKV * 128;      // bytes of one 64-column box of 128 / BKV rows
     constexpr uint32_t S_COLS = BKV, O_COL = 2 * BKV;      // tensor memory: S0 | S1 | O
     constexpr uint32_t TMEM_COLS = 256;
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* q_s = smem + L::Q_OFF;
-    unsigned char* kv_s = smem + L::KV_OFF;                // stage s: K at kv_s + s * 2 * KV_BYTES, V after it
+    unsigned char* kv_s = smem + L::KV_OFF;                // stage s: K at kv_s + s * STAGE, V after it
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;      // [2]
@@ -159,7 +171,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     // head's short rows started before the next head's long ones, and the last heads' long rows
     // ended the kernel alone: 2,048 tokens of 32 heads took 71 us where the work, evenly spread,
     // takes 41).  A sequence shorter than the longest has nothing at the highest tile numbers.
-    const int b = blockIdx.y, h = blockIdx.x;
+    const int b = blockIdx.y, hv = blockIdx.x;              // hv: (head, map)
+    const int h = hv / a.maps, map = hv - h * a.maps;
     const int tok0 = a.cu_new[b];
     const int n = a.cu_new[b + 1] - tok0;
     const int q0 = ((int)gridDim.z - 1 - (int)blockIdx.z) * BQ;
@@ -181,7 +194,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (elect_one()) {
             mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
-            for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(q_s + bx * QBOX, &q_map, h * HD + bx * 64, tok0 + q0, q_full);
+            for (int bx = 0; bx < HDK / 64; bx++) tma_load_2d(q_s + bx * QBOX, &q_map, hv * HDK + bx * 64, tok0 + q0, q_full);
             // Keys run one tile ahead of values: the keys of tile j + 1 are asked for as soon as the
             // first product of tile j - 1 has read that buffer, the values of tile j once the second
             // product of tile j - 2 has read theirs.
@@ -196,31 +209,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             auto load_k = [&](int j) -> bool {
                 const int s = j & 1;
                 if (!mbar_wait(&k_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
-                unsigned char* ks = kv_s + (size_t)s * 2 * KV_BYTES;
-                mbar_expect_tx(&k_full[s], KV_BYTES);
+                unsigned char* ks = kv_s + (size_t)s * STAGE;
+                mbar_expect_tx(&k_full[s], K_BYTES);
                 if (PAGED && j < n_old) {
                     const int y = page_row(j);
 #pragma unroll
-                    for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &kp_map, bx * 64, y, &k_full[s]);
+                    for (int bx = 0; bx < HDK / 64; bx++) tma_load_2d(ks + bx * KBOX, &kp_map, map * HDK + bx * 64, y, &k_full[s]);
                     return true;
                 }
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(ks + bx * KBOX, &k_map, kvh * HD + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &k_full[s]);
+                for (int bx = 0; bx < HDK / 64; bx++)
+                    tma_load_2d(ks + bx * KBOX, &k_map, (kvh * a.maps + map) * HDK + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &k_full[s]);
                 return true;
             };
             auto load_v = [&](int j) -> bool {
                 const int s = j & 1;
                 if (!mbar_wait(&v_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
-                unsigned char* vs = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
-                mbar_expect_tx(&v_full[s], KV_BYTES);
+                unsigned char* vs = kv_s + (size_t)s * STAGE + K_BYTES;
+                mbar_expect_tx(&v_full[s], V_BYTES);
                 if (PAGED && j < n_old) {
                     const int y = page_row(j);
 #pragma unroll
-                    for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(vs + bx * KBOX, &vp_map, bx * 64, y, &v_full[s]);
+                    for (int bx = 0; bx < HDV / 64; bx++) tma_load_2d(vs + bx * KBOX, &vp_map, bx * 64, y, &v_full[s]);
                     return true;
                 }
 #pragma unroll
-                for (int bx = 0; bx < HD / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HD + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &v_full[s]);
+                for (int bx = 0; bx < HDV / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HDV + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &v_full[s]);
                 return true;
             };
             bool ok = n_tiles > 0 && load_k(0);
@@ -232,19 +246,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     } else if (active && warp_uniform() == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc_s = instr_desc_bf16(BKV, false);    // S: N = positions, K tile K-major
-            constexpr uint32_t idesc_o = instr_desc_bf16(HD, true);      // O: N = head elements, V tile MN-major
+            constexpr uint32_t idesc_o = instr_desc_bf16(HDV, true);      // O: N = head elements, V tile MN-major
             // The one thread that issues the products is on the block's critical path: descriptors
             // are made once; inside the loop a descriptor is a base plus a constant (the address
             // field counts 16-byte units and cannot overflow within shared memory).
             const uint64_t q_desc = smem_desc_sw128(smem_u32(q_s));
-            const uint64_t k_desc0 = smem_desc_sw128(smem_u32(kv_s)), k_desc1 = smem_desc_sw128(smem_u32(kv_s + 2 * KV_BYTES));
-            const uint64_t v_desc0 = smem_desc_mn_sw128(smem_u32(kv_s + KV_BYTES), KBOX);
-            const uint64_t v_desc1 = smem_desc_mn_sw128(smem_u32(kv_s + 3 * KV_BYTES), KBOX);
+            const uint64_t k_desc0 = smem_desc_sw128(smem_u32(kv_s)), k_desc1 = smem_desc_sw128(smem_u32(kv_s + STAGE));
+            const uint64_t v_desc0 = smem_desc_mn_sw128(smem_u32(kv_s + K_BYTES), KBOX);
+            const uint64_t v_desc1 = smem_desc_mn_sw128(smem_u32(kv_s + STAGE + K_BYTES), KBOX);
             auto issue_s = [&](int j) {       // S_j = Q K_j^T into score buffer j & 1
                 const uint64_t kd = (j & 1) ? k_desc1 : k_desc0;
                 const uint32_t d = tmem + (j & 1) * S_COLS;
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; kk++)      // 64 columns per box, 32 bytes per step of 16
+                for (int kk = 0; kk < HDK / 16; kk++)     // 64 columns per box, 32 bytes per step of 16
                     tc_mma_bf16(d, q_desc + (uint64_t)(((kk >> 2) * QBOX + (kk & 3) * 32) >> 4),
                                 kd + (uint64_t)(((kk >> 2) * KBOX + (kk & 3) * 32) >> 4), idesc_s, kk > 0 ? 1u : 0u);
                 tc_commit(&s_full[j & 1]);
@@ -308,7 +322,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const int tile0 = old ? (pt_lo + j) * BKV - start : (kt_lo + j - n_old) * BKV;   // the tile's first position
             const int limit = old ? 0 : n;                                                  // where its valid keys end
             const int k0 = tile0 + half * HALF;
-            const bool edge = a.window > 0 || k0 + HALF - 1 > q0 + qd * 32 || k0 + HALF > limit;
+            // whether any of this warp's 32 rows masks any of these 32 keys: a key after the warp's first row, beyond
+            // the sequence's end, or a window or more behind the warp's last row
+            const bool edge = (a.window > 0 && k0 <= q0 + qd * 32 + 31 - a.window) || k0 + HALF - 1 > q0 + qd * 32 || k0 + HALF > limit;
             const uint32_t s_addr = tmem + sb * S_COLS + lane_base;
             // this thread's 32 scores of the row, as the product left them (the scale comes later)
             float v[HALF];
@@ -318,11 +334,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int e = 0; e < HALF; e++) v[e] = -INFINITY;
             }
+            uint32_t pk[HALF / 2];
+            float alpha = 1.f, m_new = m_used;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (MODE == 1) {
+                // w = 1 / (1 + 2^y) of y = -log2(e) (score * scale + bias[distance]), zero where the key is not visible;
+                // nothing is carried from tile to tile.  The table holds -log2(e) bias (see ti_attn_window_tc).
+                const float* hb = a.dist_bias ? a.dist_bias + (size_t)h * (a.far + 1) : nullptr;
+                const float nscale2 = -a.scale * 1.4426950408889634f;
+                if (ok && !edge && hb != nullptr && a.window > 0 && a.far >= a.window - 1) {
+                    // every key is visible to every row, so every distance is in the table: a load, a packed
+                    // multiply-add and a packed add per two scores, an exponential and a reciprocal each
+                    const float* hd = hb + (qi - k0);
+                    const unsigned long long sc2 = pack2(nscale2, nscale2), one2 = pack2(1.f, 1.f);
+#pragma unroll
+                    for (int e = 0; e < HALF; e += 2) {
+                        float e0, e1, d0, d1;
+                        unpack2(fma2(pack2(v[e], v[e + 1]), sc2, pack2(__ldg(hd - e), __ldg(hd - e - 1))), e0, e1);
+                        unpack2(add2(pack2(ex2(fminf(e0, 126.f)), ex2(fminf(e1, 126.f))), one2), d0, d1);
+                        __nv_bfloat162 t0 = __floats2bfloat162_rn(__fdividef(1.0f, d0), __fdividef(1.0f, d1));
+                        pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < HALF; e += 2) {
+                        float w[2];
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int kj = k0 + e + u;
+                            const bool vis = ok && (!edge || (kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window)));
+                            float y = v[e + u] * nscale2;
+                            if (hb) y += __ldg(hb + min(max(qi - kj, 0), a.far));
+                            w[u] = vis ? __fdividef(1.0f, 1.0f + ex2(fminf(y, 126.f))) : 0.f;
+                        }
+                        __nv_bfloat162 t0 = __floats2bfloat162_rn(w[0], w[1]);
+                        pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
+                    }
+                }
+            } else {
             if (ok && (a.cap > 0.f || a.dist_bias != nullptr)) {
                 // cap and bias work on the scaled score; what goes on from here is the result divided by the
                 // scale again, since maximum and exponent below multiply by it
                 const float inv_scale = 1.0f / a.scale, inv_cap2 = a.cap > 0.f ? 2.0f / a.cap : 0.f;
-                const float* hb = a.dist_bias ? a.dist_bias + (size_t)blockIdx.x * (a.far + 1) : nullptr;
+                const float* hb = a.dist_bias ? a.dist_bias + (size_t)h * (a.far + 1) : nullptr;
 #pragma unroll
                 for (int e = 0; e < HALF; e++) {
                     float x = v[e] * a.scale;
@@ -350,7 +404,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             mx_s[(sb * 2 + half) * BQ + r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory");      // the two warps that share these rows
             mx = fmaxf(mx, mx_s[(sb * 2 + (half ^ 1)) * BQ + r]);
-            float alpha = 1.f, m_new = m_used;
             if (mx > m_used + 8.f || (m_used == -INFINITY && mx > -INFINITY)) {
                 m_new = mx;
                 alpha = ex2(m_used - m_new);        // 0 when nothing was visible before
@@ -360,7 +413,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // packed add into the sums, one conversion to a bfloat16 pair
             const unsigned long long sc2 = pack2(scale2, scale2), nm2 = pack2(-m_sub, -m_sub);
             unsigned long long sum2[2] = {0ull, 0ull};
-            uint32_t pk[HALF / 2];
 #pragma unroll
             for (int e = 0; e < HALF; e += 4) {
                 float x0, x1, x2, x3;
@@ -373,9 +425,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 pk[e >> 1] = *reinterpret_cast<uint32_t*>(&t0);
                 pk[(e >> 1) + 1] = *reinterpret_cast<uint32_t*>(&t1);
             }
-            float sum4[4];
             unpack2(sum2[0], sum4[0], sum4[1]);
             unpack2(sum2[1], sum4[2], sum4[3]);
+            }       // MODE 0
             if (old ? (tile0 + BKV > 0 || tile0 + start < lo_blk) : (tile0 + BKV > n)) {
                 // Lines of a page outside [lo_blk, start) may hold anything (this step's tokens, an
                 // older turn of the ring, a former owner's), and the rows after a sequence's last new
@@ -389,8 +441,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     const int st = (int)threadIdx.x - 64, row = st >> 2, part = st & 3;
                     const int p = tile0 + start + row;
                     if (old ? (p < lo_blk || p >= start) : (tile0 + row >= n)) {
-                        constexpr int PART = HD / 2;        // bytes of a row's HD * 2 that one of its four threads clears
-                        uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * 2 * KV_BYTES + KV_BYTES + (part * PART / 128) * KBOX +
+                        constexpr int PART = HDV / 2;       // bytes of a row's HDV * 2 that one of its four threads clears
+                        uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * STAGE + K_BYTES + (part * PART / 128) * KBOX +
                                                               row * 128 + (part * PART) % 128);
 #pragma unroll
                         for (int e = 0; e < PART / 16; e++) dst[e] = make_uint4(0, 0, 0, 0);
@@ -410,7 +462,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     // Each half rescales its 64 of the row's 128 columns.
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); c++) {
+                    for (int c = half * (HDV / 64); c < (half + 1) * (HDV / 64); c++) {
                         float o[32];
                         tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
 #pragma unroll
@@ -432,20 +484,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             ok = __all_sync(0xffffffffu, ok);
         }
         // the row's sum: both halves'
-        l_s[half * BQ + r] = l_run;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory");      // the two warps that share these rows
-        l_run += l_s[(half ^ 1) * BQ + r];
+        if constexpr (MODE == 0) {
+            l_s[half * BQ + r] = l_run;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + qd) : "memory");      // the two warps that share these rows
+            l_run += l_s[(half ^ 1) * BQ + r];
+        }
         // the sink joins the denominator in the units of the sums: 2^(sink * log2(e) - m)
         if (a.sink != nullptr && m_used > -INFINITY) l_run += ex2(fminf(a.sink[h] * 1.4426950408889634f - m_used, 126.f));
         if (ok) {
             tc_fence_after();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* orow = (bf16*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)h * HD;
+            const float inv = MODE == 1 ? 1.f : l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* orow = (bf16*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)hv * HDV;
+            float* orow32 = (float*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)hv * HDV;
 #pragma unroll 1
-            for (int c = half * (HD / 64); c < (half + 1) * (HD / 64); c++) {
+            for (int c = half * (HDV / 64); c < (half + 1) * (HDV / 64); c++) {
                 float o[32];
                 tmem_ld32(tmem + O_COL + lane_base + c * 32, o);
-                if (qi < n) {
+                if (qi < n && a.out_f32) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4)
+                        *reinterpret_cast<float4*>(orow32 + c * 32 + e) = make_float4(o[e] * inv, o[e + 1] * inv, o[e + 2] * inv, o[e + 3] * inv);
+                } else if (qi < n) {
                     uint32_t ok4[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
@@ -510,19 +569,22 @@ int check_common(const char* what, const void* q, const void* k, const void* v, 
     return 0;
 }
 
-template <int HD, bool PAGED>
+template <int HDK, bool PAGED, int HDV = HDK, int MODE = 0>
 int launch(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& kpm, const CUtensorMap& vpm,
-           const Args& a, int n_seq, int max_new, cudaStream_t stream) {
-    constexpr size_t smem = Smem<HD>::TOTAL;
+           const Args& given, int n_seq, int max_new, cudaStream_t stream) {
+    constexpr size_t smem = Smem<HDK, HDV>::TOTAL;
     static bool configured = false;
     if (!configured) {
-        TI_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<HD, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        TI_CUDA(cudaFuncSetAttribute(attn_prefill_tc_kernel<HDK, HDV, PAGED, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     int* status = ti_status_ptr();
     TI_REQUIRE(status != nullptr, "attention_prefill: no status word");
-    dim3 grid(a.n_heads, n_seq, (max_new + BQ - 1) / BQ);
-    TI_CUDA(ti_launch(attn_prefill_tc_kernel<HD, PAGED>, grid, dim3(THREADS), smem, stream, qm, km, vm, kpm, vpm, a, status));
+    Args a = given;
+    if (a.maps < 1) a.maps = 1;
+    TI_REQUIRE((long long)a.n_heads * a.maps <= 65535, "attention_prefill: too many heads for one launch");
+    dim3 grid(a.n_heads * a.maps, n_seq, (max_new + BQ - 1) / BQ);
+    TI_CUDA(ti_launch(attn_prefill_tc_kernel<HDK, HDV, PAGED, MODE>, grid, dim3(THREADS), smem, stream, qm, km, vm, kpm, vpm, a, status));
     TI_CHECK_LAUNCH(PAGED ? "attention_chunk (tcgen05)" : "attention_prefill (tcgen05)");
     return 0;
 }
@@ -638,4 +700,61 @@ extern "C" int ti_attn_chunk_tc(const void* q, const void* k, const void* v, voi
     a.ring_rows = ring_rows; a.n_pages = n_pages;
     return head_dim == 64 ? launch<64, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)
                           : launch<128, true>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
+}
+
+// Sliding-window attention with `maps` score maps per head over keys of `dim` and values of `vdim` elements (64 or 128
+// each), softmax (mode 0) or sigmoid weights (mode 1: weight = sigmoid(score * scale + dist_bias[h][i - j]), not
+// normalised).  q [n_tokens, heads * maps * dim], k [n_tokens, kv_heads * maps * dim], v [n_tokens, kv_heads * vdim]:
+// the step's own rows as they were stored; in mode 1 dist_bias holds -log2(e) times the bias (the kernel works in powers
+// of two); out [n_tokens, heads * maps * vdim], bfloat16 or (out_f32) float32 with
+// o_stride in elements of that type.  seq_start null: every sequence starts at position 0 and the pages are not read.
+// Otherwise k_pages [pages, kv_heads, 64, maps * dim] and v_pages [pages, kv_heads, 64, vdim] hold the positions
+// before the step's.  dist_bias: float32 [heads, far + 1] or null.  window <= 0: every earlier position.
+extern "C" int ti_attn_window_tc(const void* q, const void* k, const void* v, void* out,
+                                 long long q_stride, long long k_stride, long long v_stride, long long o_stride, int out_f32,
+                                 const int* cu_new, const int* seq_start, const int* seq_slot, int n_seq, int max_new,
+                                 int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale, int window,
+                                 int mode, const void* k_pages, const void* v_pages, const int* page_table, int table_width,
+                                 int page_size, int n_pages, const float* dist_bias, int far, cudaStream_t stream) {
+    if (n_seq == 0 || max_new == 0) return 0;
+    const char* what = "attention_window (tcgen05)";
+    TI_REQUIRE((dim == 64 || dim == 128) && (vdim == 64 || vdim == 128), "%s: heads of %d and %d elements (64 or 128 each)", what, dim, vdim);
+    TI_REQUIRE(maps >= 1 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "%s: bad head counts", what);
+    TI_REQUIRE(n_seq <= 65535 && n_tokens <= 65535 * BQ, "%s: too many sequences or tokens for one launch", what);
+    TI_REQUIRE(mode == 0 || mode == 1, "%s: unknown mode %d", what, mode);
+    TI_REQUIRE(scale > 0.f && (!dist_bias || far >= 0), "%s: needs a positive scale", what);
+    TI_REQUIRE(q_stride % 8 == 0 && k_stride % 8 == 0 && v_stride % 8 == 0 && o_stride % (out_f32 ? 4 : 8) == 0,
+               "%s: token strides must be multiples of 16 bytes", what);
+    TI_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                 reinterpret_cast<uintptr_t>(out)) & 15) == 0, "%s: misaligned operands", what);
+    const bool paged = seq_start != nullptr;
+    CUtensorMap qm, km, vm, kpm, vpm;
+    if (int rc = view_map(q, n_tokens, (long long)n_heads * maps * dim, q_stride, BQ, &qm)) return rc;
+    if (int rc = view_map(k, n_tokens, (long long)n_kv_heads * maps * dim, k_stride, BKV, &km)) return rc;
+    if (int rc = view_map(v, n_tokens, (long long)n_kv_heads * vdim, v_stride, BKV, &vm)) return rc;
+    kpm = km; vpm = vm;
+    if (paged) {
+        TI_REQUIRE(k_pages && v_pages && page_table && seq_slot && table_width > 0 && n_pages > 0, "%s: incomplete cache description", what);
+        TI_REQUIRE(page_size == BKV, "%s: pages of %d positions, this kernel works on %d", what, page_size, BKV);
+        TI_REQUIRE(((reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0, "%s: cache pages must be 16-byte aligned", what);
+        const long long rows = (long long)n_pages * n_kv_heads * BKV;
+        if (int rc = view_map(k_pages, rows, (long long)maps * dim, (long long)maps * dim, BKV, &kpm)) return rc;
+        if (int rc = view_map(v_pages, rows, vdim, vdim, BKV, &vpm)) return rc;
+    }
+    Args a = {};
+    a.cu_new = cu_new; a.n_heads = n_heads; a.n_kv_heads = n_kv_heads; a.scale = scale; a.window = window > 0 ? window : 0;
+    a.out = out; a.o_stride = o_stride; a.out_f32 = out_f32; a.maps = maps;
+    a.seq_start = seq_start; a.seq_slot = seq_slot; a.page_table = page_table; a.table_width = table_width;
+    a.ring_rows = 0; a.n_pages = n_pages; a.dist_bias = dist_bias; a.far = far;
+    auto go = [&](auto dk, auto dv) -> int {
+        constexpr int DK = decltype(dk)::value, DV = decltype(dv)::value;
+        if (mode == 1) return paged ? launch<DK, true, DV, 1>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)
+                                    : launch<DK, false, DV, 1>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
+        return paged ? launch<DK, true, DV, 0>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)
+                     : launch<DK, false, DV, 0>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream);
+    };
+    using I64 = std::integral_constant<int, 64>;
+    using I128 = std::integral_constant<int, 128>;
+    if (dim == 64) return vdim == 64 ? go(I64(), I64()) : go(I64(), I128());
+    return vdim == 64 ? go(I128(), I64()) : go(I128(), I128());
 }

@@ -17,8 +17,8 @@
 // attn_window_prepare: a block per token over the projection's row [q | k | v | ...]: adds the
 //   projections' biases, norms ALL of q's and ALL of k's elements at once (x * rsqrt(mean(x^2) + eps)
 //   * w[i], a weight per element; each optional), rotates the first `rot` elements of every map of
-//   q and k by the token's position (pairs (e, e + rot/2), tables of cos and sin), writes q back
-//   in place and stores k and v at the token's position in the sequence's pages.
+//   q and k by the token's position (pairs (e, e + rot/2), tables of cos and sin), writes q, k and
+//   v back in place and stores k and v at the token's position in the sequence's pages.
 // attn_window: any number of new tokens per sequence after any number of cached ones; all keys
 //   are read from the pages, so the step's own must be stored first.  Grid (query tiles of 32,
 //   virtual heads, sequences), 128 threads: thread t works on query row t / 4; its 4 threads split
@@ -90,14 +90,16 @@ __global__ void attn_window_prepare_kernel(T* __restrict__ qkv, long long ld, co
                 x = e < half ? x * cs[e] - o * sn[e] : x * cs[e - half] + o * sn[e - half];
             }
             const T y = from_f32<T>(x);
-            if (is_q) row[i] = y;
-            else {
+            row[i] = y;         // keys and values go back too: the tensor-core kernel reads the step's own from the row
+            if (!is_q) {
                 const int g = j / kw;
                 ((T*)pg.k_pages)[(((size_t)pp * G + g) * pg.page_size + prow) * kw + (j - g * kw)] = y;
             }
         } else {
             const int j = i - nq - nk, g = j / vdim;
-            ((T*)pg.v_pages)[(((size_t)pp * G + g) * pg.page_size + prow) * vdim + (j - g * vdim)] = from_f32<T>(sm[i]);
+            const T y = from_f32<T>(sm[i]);
+            row[i] = y;
+            ((T*)pg.v_pages)[(((size_t)pp * G + g) * pg.page_size + prow) * vdim + (j - g * vdim)] = y;
         }
     }
 }

@@ -67,13 +67,36 @@ def heads_per_block(n_heads: int, n_kv: int) -> int:
     return 4 if group % 4 == 0 else 2 if group % 2 == 0 else 1
 
 
+tensor_cores = True          # tests clear this to run prompts and pieces on the CUDA-core kernel whatever their sizes
+
+
+def distance_table(r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], pb: Optional[torch.Tensor], n_heads: int, window: int,
+                   device) -> Optional[torch.Tensor]:
+    """float32 [heads, far + 1]: what a key at distance d adds to the score under the sigmoid, pb[h] - r1[h] ln(1 + r2[h] d),
+    times -log2(e) as the tensor-core kernel wants it, for every distance that a window shows (all of them share entry 0
+    without a distance term).  None when a distance term meets no window: the table would have no end."""
+    if r1 is not None and window <= 0:
+        return None
+    d = torch.arange(window if r1 is not None else 1, dtype=torch.float64, device=device)
+    t = torch.zeros((n_heads, d.numel()), dtype=torch.float64, device=device)
+    if r1 is not None:
+        t = t - r1.double()[:, None] * torch.log1p(r2.double()[:, None] * d[None, :])
+    if pb is not None:
+        t = t + pb.double()[:, None]
+    return (t * -1.4426950408889634).to(torch.float32).contiguous()      # the kernel works in powers of two: -log2(e) times the bias
+
+
 def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int, mode: str, batch,
            r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None, pb: Optional[torch.Tensor] = None,
-           out_f32: bool = False) -> torch.Tensor:
+           out_f32: bool = False, k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
+           table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [M, heads * maps, dim] (prepared) over the keys and values that ``mem`` holds, the step's own included ->
     [M, heads * maps * vdim] (float32 with ``out_f32``, else q's type).  Key j is visible to query i when
     0 <= i - j < window.  r1, r2: float32 [heads], the score loses r1 ln(1 + r2 (i - j)); pb: float32 [heads], added to
-    the score under the sigmoid.  mode: "softmax" or "sigmoid" (weights not normalised over the keys)."""
+    the score under the sigmoid.  mode: "softmax" or "sigmoid" (weights not normalised over the keys).
+    k [M, kv_heads * maps * dim], v [M, kv_heads * vdim]: the step's own keys and values as ``prepare`` left them, and
+    ``table`` (``distance_table``; sigmoid mode) let prompts and pieces run on the tensor cores: bfloat16, keys and values
+    of 64 or 128 elements each (csrc/attn_prefill_tc.cu); weights are then rounded to bfloat16 for the second product."""
     _need_cuda(q, r1, r2, pb, what="attention_window")
     M, HV, dim = q.shape
     if HV % maps or q.stride(2) != 1 or q.stride(1) != dim:
@@ -99,6 +122,18 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
               _ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(batch.seq_len), _ptr(batch.seq_slot), M, *pages,
               _ptr(r1), _ptr(r2), _ptr(pb), H, G, maps, dim, vdim, float(scale), int(window), MODES[mode], splits, _ptr(part_o),
               _ptr(part_ml), code, _stream(), launches=2 if splits > 1 else 1)
+        return out
+    if tensor_cores and q.dtype == torch.bfloat16 and dim in (64, 128) and vdim in (64, 128) and k is not None and v is not None \
+            and mem.page_size == 64 and scale > 0 and (mode == "softmax" or table is not None) and (mode == "sigmoid" or r1 is None) \
+            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 and t.stride(-1) == 1 for t in (q, k, v)):
+        if table is not None and (table.dtype != torch.float32 or table.dim() != 2 or table.shape[0] != H or not table.is_contiguous()):
+            raise KernelError("attention_window: the distance table must be dense float32 [heads, far + 1]")
+        start = batch.mode == "start"
+        _call(_fn("ti_attn_window_tc", [P, P, P, P, L, L, L, L, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, I, P, I, P]),
+              _ptr(q), _ptr(k), _ptr(v), _ptr(out), q.stride(0), k.stride(0), v.stride(0), out.stride(0), 1 if out_f32 else 0,
+              _ptr(batch.cu_new), None if start else _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, M, H, G,
+              maps, dim, vdim, float(scale), int(window), MODES[mode], *pages, _ptr(table) if mode == "sigmoid" else None,
+              table.shape[1] - 1 if (mode == "sigmoid" and table is not None) else 0, _stream())
         return out
     _call(_fn("ti_attn_window", [P, L, P, L, I, P, P, P, I, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, F, I, I, I, P]),
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(batch.cu_new), _ptr(batch.seq_start),

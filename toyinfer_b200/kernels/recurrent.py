@@ -152,12 +152,16 @@ def block_diag_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return out
 
 
+SSD_SEGMENT = 256               # tokens of a segment; a step whose longest sequence brings two or more runs them in parallel
+
+
 def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, rate: torch.Tensor, skip: Optional[torch.Tensor],
              n_heads: int, groups: int, n_state: int, vdim: int, state: torch.Tensor, state_offset: int, batch) -> torch.Tensor:
     """The Mamba-2 recurrence over every sequence's new tokens (csrc/ssd_scan.cu).  xbc [M, heads * vdim + 2 * groups *
     n_state]: x, B and C after their convolution and silu; dt_raw [M, heads] the raw step sizes (rows may be strided);
     dt_bias, rate (= exp(A_log)) and skip float32 [heads].  Returns float32 y [M, heads * vdim]; the state
-    [heads, vdim, n_state] per slot is left as it is after the step's tokens."""
+    [heads, vdim, n_state] per slot is left as it is after the step's tokens.  Sequences that bring more than
+    ``2 * SSD_SEGMENT`` tokens run as segments in parallel (three launches)."""
     _need_cuda(xbc, dt_raw, dt_bias, rate, skip, state, what="ssd_scan")
     M = xbc.shape[0]
     inner = n_heads * vdim
@@ -169,10 +173,16 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, rat
         _vec(t, n_heads, f"ssd_scan: the {what}")
     base, stride = _state_part(state, state_offset, inner * n_state, "ssd_scan")
     y = torch.zeros((M, inner), dtype=torch.float32, device=xbc.device)         # rows that are nobody's stay zero
-    _call(_fn("ti_ssd_scan", [P, L, P, L, P, P, P, P, L, P, P, P, I, I, I, I, I, I, P]),
+    seg = int(SSD_SEGMENT)
+    n_seg = (batch.max_new + seg - 1) // seg if batch.max_new >= 2 * seg else 1
+    scratch = decay = None
+    if n_seg > 1:
+        scratch = torch.empty((batch.n_seq * n_seg, inner * n_state), dtype=torch.float32, device=xbc.device)
+        decay = torch.empty((batch.n_seq * n_seg, n_heads), dtype=torch.float32, device=xbc.device)
+    _call(_fn("ti_ssd_scan", [P, L, P, L, P, P, P, P, L, P, P, P, I, I, I, I, I, I, I, P, P, I, P]),
           _ptr(xbc), xbc.stride(0), _ptr(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(rate), _ptr(skip), base, stride, _ptr(y),
-          _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, int(n_heads), int(groups), int(n_state), int(vdim),
-          _code(xbc, "ssd_scan"), _stream())
+          _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, int(n_heads), int(groups), int(n_state), int(vdim), seg, n_seg,
+          _ptr(scratch), _ptr(decay), _code(xbc, "ssd_scan"), _stream(), launches=3 if n_seg > 1 else 1)
     return y
 
 

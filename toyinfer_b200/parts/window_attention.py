@@ -80,7 +80,7 @@ class SigmoidAttention(_WindowAttention):
              "bias": ".b"}
         n.update(names or {})
         self.n = n
-        self.w_qkv = self.w_o = self.b_qkv = self.q_w = self.k_w = self.r1 = self.r2 = self.pb = None
+        self.w_qkv = self.w_o = self.b_qkv = self.q_w = self.k_w = self.r1 = self.r2 = self.pb = self.table = None
 
     def _name(self, k: str, bias: bool = False) -> str:
         return self.prefix + self.n[k] + (self.n["bias"] if bias else "")
@@ -116,6 +116,8 @@ class SigmoidAttention(_WindowAttention):
             self.r1, self.r2 = f32(self._name("r1")), f32(self._name("r2"))
         if self.head_bias:
             self.pb = f32(self._name("pb"))
+        # what a distance adds under the sigmoid, for the tensor-core kernel: a row per head as long as the window
+        self.table = KW.distance_table(self.r1, self.r2, self.pb, self.n_heads, self.window, self.w_o.device)
 
     def forward(self, x, batch, mem, shared) -> torch.Tensor:
         self._memory(mem)
@@ -126,7 +128,8 @@ class SigmoidAttention(_WindowAttention):
         with ranged(batch, "mixer.attention"):
             KW.prepare(qkv, self.b_qkv, self.q_w, self.k_w, self.eps, None, H, G, 1, d, vd, mem, batch)
             a = KW.attend(qkv[:, :H * d].view(M, H, d), 1, vd, mem, self.scale, self.window, "sigmoid", batch,
-                          r1=self.r1, r2=self.r2, pb=self.pb)
+                          r1=self.r1, r2=self.r2, pb=self.pb, k=qkv[:, H * d:(H + G) * d], v=qkv[:, (H + G) * d:(H + G) * d + G * vd],
+                          table=self.table)
         with ranged(batch, "mixer.out"):
             return K.linear(a, self.w_o)
 
@@ -164,7 +167,12 @@ class DiffAttention(_WindowAttention):
         t = lambda k: tensors.pop(self.names[k])
         f64 = lambda k: t(k).to(torch.float64)
         # q, k, v and the gate's rows as one matrix: one product per token row
-        self.w_in = torch.cat([t(k) for k in (("q", "k", "v", "g") if self.gate else ("q", "k", "v"))], dim=0).contiguous()
+        # (rows of zeros bring the product's rows to a multiple of 16 bytes, which the tensor-core kernel's loads need)
+        parts = [t(k) for k in (("q", "k", "v", "g") if self.gate else ("q", "k", "v"))]
+        spare = -sum(p.shape[0] for p in parts) % 8
+        if spare:
+            parts.append(torch.zeros((spare, self.hidden), dtype=parts[0].dtype, device=parts[0].device))
+        self.w_in = torch.cat(parts, dim=0).contiguous()
         self.w_o = t("o").contiguous()
         self.lam = math.exp(float((f64("lq1") * f64("lk1")).sum())) - math.exp(float((f64("lq2") * f64("lk2")).sum())) + self.diff
 
@@ -178,8 +186,9 @@ class DiffAttention(_WindowAttention):
         with ranged(batch, "mixer.attention"):
             tables = self.position.rotary_tables() if self.position is not None else None
             KW.prepare(qkvg, None, None, None, self.eps, tables, H, G, 2, d, vd, mem, batch)
-            a = KW.attend(qkvg[:, :nq].view(M, 2 * H, d), 2, vd, mem, self.scale, self.window, "softmax", batch, out_f32=True)
-            o = KW.diff_combine(a, qkvg[:, nq + nkv:] if self.gate else None, H, vd, self.lam, self.diff, self.eps, qkvg.dtype)
+            a = KW.attend(qkvg[:, :nq].view(M, 2 * H, d), 2, vd, mem, self.scale, self.window, "softmax", batch, out_f32=True,
+                          k=qkvg[:, nq:nq + G * 2 * d], v=qkvg[:, nq + G * 2 * d:nq + nkv])
+            o = KW.diff_combine(a, qkvg[:, nq + nkv:nq + nkv + H] if self.gate else None, H, vd, self.lam, self.diff, self.eps, qkvg.dtype)
         with ranged(batch, "mixer.out"):
             return K.linear(o, self.w_o)
 
