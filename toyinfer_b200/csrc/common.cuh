@@ -155,6 +155,16 @@ static inline cudaError_t ti_launch_after(void (*kernel)(KArgs...), dim3 grid, d
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The activation of a gated product's gate.  kind 1: silu, z / (1 + exp(-z)); kind 2: the tanh form of gelu,
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float ti_gate_act(float z, int kind) {
+    if (kind == 2) {
+        const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+        return 0.5f * z * (1.0f + tanhf(u));
+    }
+    return z / (1.0f + expf(-z));
+}
+
 template <typename F>
 static inline int ti_dispatch_dtype(int dtype, F&& f) {
     // f is called with a value of the element type

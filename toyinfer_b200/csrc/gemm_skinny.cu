@@ -50,7 +50,7 @@ struct Args {
 };
 
 // NT: token tiles of 8 (1 or 2); WARPS per block; WPR: warps that share a group of 16 rows.
-template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
+template <int NT, int WARPS, int WPR, int GATED, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel(Args a) {
     ti_pdl_trigger();
     __shared__ float part[WPR > 1 ? WARPS * NT * 4 * 32 : 1];
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
                     const int tok = n * 8 + 2 * t + (e & 1);
                     if (in_group + 1 < R && row + 1 < a.N && tok < a.M) {
                         const float gate = c[n][e], up = other[e];
-                        out[(size_t)tok * a.ldo + (size_t)(row >> 1)] = from_f32<OutT>(up * (gate / (1.f + expf(-gate))));
+                        out[(size_t)tok * a.ldo + (size_t)(row >> 1)] = from_f32<OutT>(up * ti_gate_act(gate, GATED));
                     }
                 }
             }
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
 
 int rows_per_group(int N, long long places, bool gated);
 
-template <int NT, int WARPS, int WPR, bool GATED, typename OutT>
+template <int NT, int WARPS, int WPR, int GATED, typename OutT>
 int launch(Args a, int sms, bool late_start, cudaStream_t stream) {
     // blocks of this kernel that an SM holds at once, as the runtime counts them (asked once)
     static int per_sm = 0;
@@ -181,7 +181,7 @@ int launch(Args a, int sms, bool late_start, cudaStream_t stream) {
     return 0;
 }
 
-template <int NT, bool GATED, typename OutT>
+template <int NT, int GATED, typename OutT>
 int launch_wpr(const Args& a, int wpr, int sms, bool late_start, cudaStream_t stream) {
     switch (wpr) {
         case 1: return launch<NT, 8, 1, GATED, OutT>(a, sms, late_start, stream);
@@ -194,7 +194,8 @@ int launch_wpr(const Args& a, int wpr, int sms, bool late_start, cudaStream_t st
 
 template <int NT>
 int launch_nt(const Args& a, int out_f32, int gated, int wpr, int sms, bool late_start, cudaStream_t stream) {
-    if (gated) return launch_wpr<NT, true, bf16>(a, wpr, sms, late_start, stream);
+    if (gated == 2) return launch_wpr<NT, 2, bf16>(a, wpr, sms, late_start, stream);
+    if (gated) return launch_wpr<NT, 1, bf16>(a, wpr, sms, late_start, stream);
     if (out_f32) return launch_wpr<NT, false, float>(a, wpr, sms, late_start, stream);
     return launch_wpr<NT, false, bf16>(a, wpr, sms, late_start, stream);
 }

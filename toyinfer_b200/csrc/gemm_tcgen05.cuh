@@ -13,7 +13,7 @@ struct GemmArgs {
     int rows_a, rows_b, K;
     void* out; long long ld_out; int out_f32; int transposed;
     int splits; float* workspace; int* tickets;
-    int gated;      // rows of the weight operand come in (gate, up) pairs: store up * silu(gate), half as many columns
+    int gated;      // rows of the weight operand come in (gate, up) pairs: store up * act(gate), half as many columns (1: silu, 2: gelu, tanh form)
     int shared_tiles;   // many-token kernel: the first so many tiles are shared out by contraction steps (see TileWalk)
 };
 
@@ -39,7 +39,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& g, int i, int b0, in
                 const int j = b0 + c + e;
                 if ((lane & 1) == 0 && i < g.rows_a && j < g.rows_b)
                     ((bf16*)g.out)[(size_t)j * g.ld_out + (i >> 1)] =
-                        __float2bfloat16_rn(other * (mine / (1.0f + expf(-mine))));
+                        __float2bfloat16_rn(other * ti_gate_act(mine, g.gated));
             }
         } else if (i < g.rows_a) {
             const int j0 = b0 + c;
@@ -50,7 +50,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& g, int i, int b0, in
             for (int e = 0; e < 8; e++) {
                 const float gate = __bfloat162float(__float2bfloat16_rn(r[2 * e]));
                 const float up = __bfloat162float(__float2bfloat16_rn(r[2 * e + 1]));
-                z[e] = up * (gate / (1.0f + expf(-gate)));
+                z[e] = up * ti_gate_act(gate, g.gated);
             }
             if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll

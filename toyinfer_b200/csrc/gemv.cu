@@ -48,7 +48,7 @@ __device__ __forceinline__ void fma_piece(float (&acc)[M], const uint4& wv, cons
     }
 }
 
-template <int M, int R, int U, int WPR, bool GATED, typename OutT>
+template <int M, int R, int U, int WPR, int GATED, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(const bf16* x, const bf16* __restrict__ w, OutT* __restrict__ out, int N, int K,
             long long ldx, long long ldw, long long ldo) {
@@ -116,7 +116,7 @@ gemv_kernel(const bf16* x, const bf16* __restrict__ w, OutT* __restrict__ out, i
 #pragma unroll
             for (int m = 0; m < M; m++) {
                 const float g = acc[r][m], up = acc[r + 1][m];
-                out[(size_t)m * ldo + (size_t)((row0 + r) >> 1)] = from_f32<OutT>(up * (g / (1.f + expf(-g))));
+                out[(size_t)m * ldo + (size_t)((row0 + r) >> 1)] = from_f32<OutT>(up * ti_gate_act(g, GATED));
             }
         }
     } else {
@@ -134,7 +134,7 @@ gemv_kernel(const bf16* x, const bf16* __restrict__ w, OutT* __restrict__ out, i
 // of h and delta come from L2, and the step loses a kernel whose whole work was this.  The sums run
 // as in the row-wise kernel (elementwise.cu: rmsnorm_kernel), thread for thread, so both ways
 // give the same bits.  Block 0 stores the rounded sum to h_out, the next reader's hidden state.
-template <int R, int U, int WPR, bool GATED, typename NW>
+template <int R, int U, int WPR, int GATED, typename NW>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_normed_kernel(const bf16* h, const bf16* delta, const NW* __restrict__ g, float eps, bf16* __restrict__ h_out,
                    const bf16* __restrict__ w, bf16* __restrict__ out, int N, int K, long long ldw) {
@@ -244,7 +244,7 @@ gemv_normed_kernel(const bf16* h, const bf16* delta, const NW* __restrict__ g, f
         for (int r = 0; r < R; r += 2) {
             if (row0 + r + 1 >= N) break;
             const float gt = acc[r][0], up = acc[r + 1][0];
-            out[(size_t)((row0 + r) >> 1)] = __float2bfloat16_rn(up * (gt / (1.f + expf(-gt))));
+            out[(size_t)((row0 + r) >> 1)] = __float2bfloat16_rn(up * ti_gate_act(gt, GATED));
         }
     } else {
 #pragma unroll
@@ -259,7 +259,7 @@ struct Args {
     const bf16* x; const bf16* w; void* out; int N, K; long long ldx, ldw, ldo; cudaStream_t stream;
 };
 
-template <int M, int R, int WPR, bool GATED, typename OutT>
+template <int M, int R, int WPR, int GATED, typename OutT>
 int launch(const Args& a, bool late_start) {
     constexpr int U = R == 2 ? 4 : 2;          // 128 bytes of weights in flight per lane either way
     const long long groups = ((long long)a.N + R - 1) / R;
@@ -275,7 +275,7 @@ int launch(const Args& a, bool late_start) {
     return 0;
 }
 
-template <int M, int R, bool GATED, typename OutT>
+template <int M, int R, int GATED, typename OutT>
 int launch_wpr(const Args& a, int wpr, bool late_start) {
     switch (wpr) {
         case 1: return launch<M, R, 1, GATED, OutT>(a, late_start);
@@ -285,14 +285,15 @@ int launch_wpr(const Args& a, int wpr, bool late_start) {
     }
 }
 
-template <int M, bool GATED, typename OutT>
+template <int M, int GATED, typename OutT>
 int launch_r(const Args& a, int rows, int wpr, bool late_start) {
     return rows == 4 ? launch_wpr<M, 4, GATED, OutT>(a, wpr, late_start) : launch_wpr<M, 2, GATED, OutT>(a, wpr, late_start);
 }
 
 template <int M>
 int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr, bool late_start) {
-    if (gated) return launch_r<M, true, bf16>(a, rows, wpr, late_start);
+    if (gated == 2) return launch_r<M, 2, bf16>(a, rows, wpr, late_start);
+    if (gated) return launch_r<M, 1, bf16>(a, rows, wpr, late_start);
     if (out_f32) return launch_r<M, false, float>(a, rows, wpr, late_start);
     return launch_r<M, false, bf16>(a, rows, wpr, late_start);
 }
@@ -323,7 +324,7 @@ struct NormedArgs {
     const bf16* w; bf16* out; int N, K; long long ldw; cudaStream_t stream;
 };
 
-template <int R, int WPR, bool GATED, typename NW>
+template <int R, int WPR, int GATED, typename NW>
 int launch_normed(const NormedArgs& a) {
     constexpr int U = R == 2 ? 4 : 2;
     const long long groups = ((long long)a.N + R - 1) / R;
@@ -334,7 +335,7 @@ int launch_normed(const NormedArgs& a) {
     TI_CHECK_LAUNCH("linear (one token, norm inside)");
     return 0;
 }
-template <int R, bool GATED, typename NW>
+template <int R, int GATED, typename NW>
 int launch_normed_wpr(const NormedArgs& a, int wpr) {
     switch (wpr) {
         case 1: return launch_normed<R, 1, GATED, NW>(a);
@@ -343,7 +344,7 @@ int launch_normed_wpr(const NormedArgs& a, int wpr) {
         default: return launch_normed<R, 8, GATED, NW>(a);
     }
 }
-template <bool GATED, typename NW>
+template <int GATED, typename NW>
 int launch_normed_r(const NormedArgs& a, int rows, int wpr) {
     return rows == 4 ? launch_normed_wpr<4, GATED, NW>(a, wpr) : launch_normed_wpr<2, GATED, NW>(a, wpr);
 }
@@ -385,6 +386,6 @@ extern "C" int ti_linear_gemv_normed(const void* h, const void* delta, const voi
     int rows, wpr;
     choose_shape(1, N, K, sms, &rows, &wpr);
     NormedArgs a{(const bf16*)h, (const bf16*)delta, g, eps, (bf16*)h_out, (const bf16*)w, (bf16*)out, N, K, ldw, stream};
-    if (g_is_f32) return gated ? launch_normed_r<true, float>(a, rows, wpr) : launch_normed_r<false, float>(a, rows, wpr);
-    return gated ? launch_normed_r<true, bf16>(a, rows, wpr) : launch_normed_r<false, bf16>(a, rows, wpr);
+    if (g_is_f32) return gated ? launch_normed_r<1, float>(a, rows, wpr) : launch_normed_r<0, float>(a, rows, wpr);
+    return gated ? launch_normed_r<1, bf16>(a, rows, wpr) : launch_normed_r<0, bf16>(a, rows, wpr);
 }

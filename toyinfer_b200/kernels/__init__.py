@@ -284,12 +284,15 @@ def swiglu(gu: torch.Tensor, pairs: bool = False) -> torch.Tensor:
     return out
 
 
-def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """x[M, K] times w_pairs[2*I, K] (rows gate_0, up_0, gate_1, up_1, ...) followed by the
-    gated activation -> [M, I].  The activation runs in the product's epilogue where the
-    tensor-core kernel takes the shape, else as a kernel of its own.  x may be a PendingNorm."""
+    gated activation act(gate) * up -> [M, I]; act "silu" or "gelu_tanh".  The activation runs in the
+    product's epilogue where the tensor-core kernel takes the shape, else as a kernel of its own.
+    x may be a PendingNorm."""
+    if act not in GATE_ACTS:
+        raise KernelError(f"linear_swiglu: unknown activation {act!r}; known: {sorted(GATE_ACTS)}")
     if isinstance(x, PendingNorm):
-        out = _linear_pending(x, w_pairs, gated=True) if w_pairs.dim() == 2 and w_pairs.shape[0] % 2 == 0 else None
+        out = _linear_pending(x, w_pairs, gated=True) if act == "silu" and w_pairs.dim() == 2 and w_pairs.shape[0] % 2 == 0 else None
         if out is not None:
             return out
         x = x.tensor()
@@ -304,9 +307,9 @@ def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor) -> torch.Tensor:
     ldx, ldw = _row_stride(x, "linear x"), _row_stride(w_pairs, "linear w")
     if gemm.tc_eligible(x, w_pairs, K, ldx, ldw):
         out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
-        gemm.run(x, w_pairs, out, M, N, K, ldx, ldw, gated=True)
+        gemm.run(x, w_pairs, out, M, N, K, ldx, ldw, gated=1 + GATE_ACTS[act])      # the kernels' codes: 1 silu, 2 gelu
         return out
-    return swiglu(linear(x, w_pairs), pairs=True)
+    return swiglu(linear(x, w_pairs), pairs=True) if act == "silu" else gated_act(linear(x, w_pairs), act, pairs=True)
 
 
 def qk_norm_rope_store(q, k, v, q_w, k_w, eps, tables, batch, mem) -> None:

@@ -57,8 +57,8 @@ register_part("feed_forward", "swiglu", SwiGLU)
 
 class GatedDense(FeedForward):
     """y = Wdown (act(Wgate x) * (Wup x)) with ``act`` "gelu_tanh" or "silu"; no bias.  Gate and up rows are one matrix
-    (gate's rows, then up's), so one product makes both; the activation and the product of the two halves run in 32-bit
-    with one rounding (kernels.gated_act).  With "silu" this is the SwiGLU above without its paired rows."""
+    with row 2i the gate's and row 2i + 1 the up's i-th, so one product makes both and the activation runs in that
+    product's epilogue on the tensor-core kernels (kernels.linear_swiglu), in 32-bit with one rounding."""
 
     captures_start = True
 
@@ -80,11 +80,12 @@ class GatedDense(FeedForward):
                 self.names["down"]: ParamSpec((self.hidden, self.inter), std=0.05)}
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.w_gate_up = torch.cat([tensors.pop(self.names["gate"]), tensors.pop(self.names["up"])], dim=0).contiguous()
+        g, u = tensors.pop(self.names["gate"]), tensors.pop(self.names["up"])
+        self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.inter, self.hidden).contiguous()
         self.w_down = tensors.pop(self.names["down"]).contiguous()
 
     def forward(self, x, batch) -> torch.Tensor:
-        return K.linear(K.gated_act(K.linear(x, self.w_gate_up), self.act), self.w_down)
+        return K.linear(K.linear_swiglu(x, self.w_gate_up, self.act), self.w_down)
 
 
 class SquaredReLU(FeedForward):
