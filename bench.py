@@ -642,9 +642,13 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             N, Kd = {"gemm_head": (151936, H), "gemm_down": (H, I), "gemm_qkv": (6144, H), "gemm_o": (H, 4096)}.get(name, (2 * I, H))
             x, w = rnd(M, Kd), rnd(N, Kd, scale=0.02)
             return (lambda: K.linear(x, w)), (N * Kd + M * Kd + M * N) * 2, 2.0 * M * N * Kd
-        if name in ("attn_decode", "attn_decode_b64", "attn_decode_b1"):
-            B, ctx = {"attn_decode": (8, 8192), "attn_decode_b64": (64, 2048), "attn_decode_b1": (1, 2048)}[name]
+        if name in ("attn_decode", "attn_decode_b64", "attn_decode_b1") or name.startswith("attn_decode:"):
             nh, nkv, hd = 32, 8, 128
+            if ":" in name:                                # attn_decode:BATCH,CONTEXT[,HEADS,KV_HEADS]
+                B, ctx, *hs = (int(v) for v in name.split(":")[1].split(","))
+                nh, nkv = hs if hs else (nh, nkv)
+            else:
+                B, ctx = {"attn_decode": (8, 8192), "attn_decode_b64": (64, 2048), "attn_decode_b1": (1, 2048)}[name]
             pages = B * ctx // 64
             table = (torch.arange(pages, dtype=torch.int32, device=dev).view(B, ctx // 64) + 1)
             table = torch.cat([table, torch.zeros(1, ctx // 64, dtype=torch.int32, device=dev)]).contiguous()
@@ -698,6 +702,27 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(1, new, dev), "mixed", [0], [cached], [[0] * new], 1, cached + new)
             return (lambda: K.attention_chunk(q, k, v, mem, 1 / math.sqrt(hd), 0, batch)), \
                 qkv.numel() * 2 + new * nh * hd * 2 + 2 * cached * nkv * hd * 2, 4.0 * nh * hd * new * (cached + (new + 1) / 2)
+        if name.startswith("attn_window_decode"):         # attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]]: one token per sequence
+            from toyinfer_b200.kernels import attention_window as KW
+            opts = name.split(":")[1].split(",") if ":" in name else []
+            B, ctx = (int(opts[0]), int(opts[1])) if len(opts) > 1 else (8, 2048)
+            kind = opts[2] if len(opts) > 2 else "sigmoid"
+            window = int(opts[3]) if len(opts) > 3 else 1024
+            nh, nkv = 16, 4
+            maps, hd, vd = (1, 128, 128) if kind == "sigmoid" else (2, 64, 128)
+            per = (ctx + 63) // 64
+            table = (torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per) + 1)
+            table = torch.cat([table, torch.zeros(1, per, dtype=torch.int32, device=dev)]).contiguous()
+            mem = KVView(rnd(B * per + 1, nkv, 64, maps * hd), rnd(B * per + 1, nkv, 64, vd), table, nkv, maps * hd, 0, 0)
+            batch = fill_batch(BatchBuffers(B, B, dev), "extend", list(range(B)), [ctx - 1] * B, [[0]] * B, B, ctx)
+            q = rnd(B, nh * maps, hd)
+            f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
+            r1, r2, pb = (f32(nh), f32(nh), -2 * f32(nh)) if kind == "sigmoid" else (None, None, None)
+            seen = min(ctx, window)
+            # the visible keys and values are read once per kv head
+            return (lambda: KW.attend(q, maps, vd, mem, hd ** -0.5, window, "sigmoid" if kind == "sigmoid" else "softmax", batch,
+                                      r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid")), \
+                B * seen * nkv * (maps * hd + vd) * 2, 2.0 * B * seen * nh * maps * (hd + vd)
         if name.startswith("attn_window"):                # attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]]: a whole prompt
             from toyinfer_b200.kernels import attention_window as KW
             opts = name.split(":")[1].split(",") if ":" in name else []
@@ -723,6 +748,19 @@ def run_kernel(name: str, reps: int, eager: bool = False):
                                       "sigmoid" if kind == "sigmoid" else "softmax", batch, r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid",
                                       k=qkv[:, nq:nq + nk], v=qkv[:, nq + nk:], table=tab)), \
                 qkv.numel() * 2 + T * nh * maps * vd * (2 if kind == "sigmoid" else 4), 2.0 * nh * maps * (hd + vd) * pairs
+        if name.startswith("ssd_decode"):                 # ssd_decode[:BATCH]: one token per sequence through the Mamba-2 recurrence
+            from toyinfer_b200.kernels import recurrent as KR
+            B = int(name.split(":")[1]) if ":" in name else 8
+            heads, vd, N, groups = 64, 64, 128, 8
+            inner = heads * vd
+            xbc, dt = rnd(B, inner + 2 * groups * N), rnd(B, heads)
+            f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
+            dt_bias, rate, skip = f32(heads) - 1.0, f32(heads) + 0.5, f32(heads)
+            state = torch.zeros(B + 1, inner * N, dtype=torch.float32, device=dev)
+            batch = fill_batch(BatchBuffers(B, B, dev), "extend", list(range(B)), [100] * B, [[0]] * B, B, 101)
+            # every sequence's float32 state is read and written once
+            return (lambda: KR.ssd_scan(xbc, dt, dt_bias, rate, skip, heads, groups, N, vd, state, 0, batch)), \
+                2 * B * inner * N * 4, 4.0 * B * inner * N
         if name.startswith("ssd_scan"):                   # ssd_scan[:TOKENS[,SEGMENT]]: the Mamba-2 recurrence over one prompt
             from toyinfer_b200.kernels import recurrent as KR
             opts = name.split(":")[1].split(",") if ":" in name else []
@@ -789,9 +827,10 @@ def main() -> int:
     ap.add_argument("--range", action="store_true",
                     help="also the mean decode rate while the batch grows from 2,048 positions to --context (some 20 s more)")
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
-                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K[,BN,SPLITS], attn_decode, attn_decode_b64, attn_decode_b1, "
+                    "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K[,BN,SPLITS], attn_decode[:BATCH,CONTEXT[,HEADS,KV_HEADS]], attn_decode_b64, attn_decode_b1, "
                     "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], "
-                    "attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]], ssd_scan[:TOKENS[,SEGMENT]], mma_issue; "
+                    "attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]], attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]], "
+                    "ssd_scan[:TOKENS[,SEGMENT]], ssd_decode[:BATCH], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")

@@ -96,12 +96,27 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long ld_xbc, const T* __restrict
     for (int c = 0; c < CPT; c++)
 #pragma unroll
         for (int r = 0; r < R; r++) S[c][r] = 0.f;
+    // a lane's R values of a column are read and written 16 bytes at a time where the column holds all of them and starts
+    // on such a boundary (a step of single tokens is this read and this write and little else)
+    const bool whole = R >= 4 && N % 4 == 0 && slot_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0 &&
+                       (!scratch || (reinterpret_cast<uintptr_t>(scratch) & 15) == 0) && sub * R + R <= N;
     if (OUT) {
         const float* from = scratch ? scratch + (size_t)(b * n_seg + p) * per_slot + at : slot_st;
 #pragma unroll
-        for (int c = 0; c < CPT; c++)
+        for (int c = 0; c < CPT; c++) {
+            if constexpr (R >= 4) {
+                if (whole && v + c < vdim) {
+#pragma unroll
+                    for (int r = 0; r < R; r += 4) {
+                        const float4 q = __ldcs(reinterpret_cast<const float4*>(from + (size_t)c * N + sub * R + r));
+                        S[c][r] = q.x; S[c][r + 1] = q.y; S[c][r + 2] = q.z; S[c][r + 3] = q.w;
+                    }
+                    continue;
+                }
+            }
 #pragma unroll
             for (int r = 0; r < R; r++) S[c][r] = (v + c < vdim && sub * R + r < N) ? from[(size_t)c * N + sub * R + r] : 0.f;
+        }
     }
     const T* Bg = xbc + inner + (size_t)g * N;
     const T* Cg = xbc + inner + (size_t)(groups + g) * N;
@@ -216,10 +231,19 @@ ssd_scan_kernel(const T* __restrict__ xbc, long long ld_xbc, const T* __restrict
     float* to = OUT ? (last ? slot_st : nullptr) : scratch + (size_t)(b * n_seg + p + 1) * per_slot + at;
     if (to != nullptr) {
 #pragma unroll
-        for (int c = 0; c < CPT; c++)
+        for (int c = 0; c < CPT; c++) {
+            if constexpr (R >= 4) {
+                if (whole && v + c < vdim) {
+#pragma unroll
+                    for (int r = 0; r < R; r += 4)
+                        *reinterpret_cast<float4*>(to + (size_t)c * N + sub * R + r) = make_float4(S[c][r], S[c][r + 1], S[c][r + 2], S[c][r + 3]);
+                    continue;
+                }
+            }
 #pragma unroll
             for (int r = 0; r < R; r++)
                 if (v + c < vdim && sub * R + r < N) to[(size_t)c * N + sub * R + r] = S[c][r];
+        }
     }
     if (!OUT && blockIdx.x == 0 && tid == 0) seg_decay[(size_t)(b * n_seg + p) * heads + h] = (float)exp(log_decay);
 }
