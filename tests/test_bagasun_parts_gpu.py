@@ -223,6 +223,51 @@ def test_tensor_core_prompts_and_pieces_agree_with_the_cuda_core_kernel(kind, c,
     assert "ti_attn_window_tc" not in calls
 
 
+@pytest.mark.parametrize("kind,c", [
+    ("sigmoid", dict(n_heads=8, n_kv_heads=2, dim=64, vdim=64, window=0)),                    # every earlier key
+    ("sigmoid", dict(n_heads=20, n_kv_heads=1, dim=128, vdim=128, window=150)),               # more heads than one block's sixteen rows
+    ("sigmoid", dict(n_heads=3, n_kv_heads=3, dim=64, vdim=64, window=1)),
+    ("diff", dict(n_heads=10, n_kv_heads=1, dim=64, vdim=128, window=300, rot=32, diff=0.2,
+                  scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 256})),       # twenty score maps on one kv head
+    ("diff", dict(n_heads=2, n_kv_heads=2, dim=32, vdim=64, window=0, rot=0, scaling=None, diff=0.5)),
+    ("diff", dict(n_heads=4, n_kv_heads=2, dim=64, vdim=128, window=65, rot=64, scaling=None, diff=0.7)),
+])
+def test_single_tokens_on_the_tensor_core_kernel(kind, c, monkeypatch):
+    """bfloat16 and a key row as long as a value row (64 or 128 elements): single tokens run on the dense model's
+    tensor-core kernel under this design's score rules (sigmoid weights with the distance term; two maps that share a key
+    row, float32 results).  Two sequences of unequal length go on token by token from 450 and 75 positions, far enough for
+    the longer one's keys to be split over blocks and merged where the window shows that many; loud rows stand where the
+    windows end and at page borders.  The
+    result is held against the plain implementation and against the CUDA-core kernel."""
+    from toyinfer_b200.kernels import attention_window as KW
+    dtype = torch.bfloat16
+    m, w, mcfg = (make_sigmoid if kind == "sigmoid" else make_diff)(dtype, c)
+    calls = []
+    real = KW._fn
+
+    def spy(name, sig):
+        calls.append(name)
+        return real(name, sig)
+    monkeypatch.setattr(KW, "_fn", spy)
+    lens, steps = [500, 125], 50
+    loud = [0, 63, 64, 150, 151, 200, 201, 300, 301, 349, 350, 385, 386, 448, 460]
+    xs = [loud_inputs(n, 56, 60 + i, [j for j in loud if j < n], 6.0).to(dtype) for i, n in enumerate(lens)]
+    fn = plain.sigmoid_attention if kind == "sigmoid" else plain.diff_attention
+    wants = [fn(x.double(), w, mcfg, 1e-5) for x in xs]
+    sched = [[(0, lens[0] - steps), (1, lens[1] - steps)]] + [[(0, 1), (1, 1)] for _ in range(steps)]
+    got = feed(m, m.memory_request(), xs, sched, dtype)
+    assert "ti_attn_decode_mma_scored" in calls and "ti_attn_window_decode" not in calls
+    assert ("ti_attn_window_merge" in calls) == (c["window"] in (0, 300))
+    for g, want in zip(got, wants):
+        torch.testing.assert_close(g[-steps:], want[-steps:], **tol(dtype, 30.0 if kind == "sigmoid" else 3.0))
+    monkeypatch.setattr(KW, "tensor_cores", False)
+    calls.clear()
+    slow = feed(m, m.memory_request(), xs, sched, dtype)
+    assert "ti_attn_window_decode" in calls and "ti_attn_decode_mma_scored" not in calls
+    for i, (g, x) in enumerate(zip(got, slow)):
+        torch.testing.assert_close(g[-steps:], x[-steps:], rtol=3e-2, atol=0.15, msg=lambda e: f"{kind}, sequence {i}: {e}")
+
+
 @pytest.mark.parametrize("dtype", DT)
 def test_differential_attention_without_a_gate(dtype):
     c = DIFF[0]

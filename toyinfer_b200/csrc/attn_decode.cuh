@@ -15,6 +15,14 @@ struct DecodeArgs {
     float scale;
     void* out; long long o_stride;            // [B, heads, hd]
     float* part_o; float* part_ml;            // [B, heads, splits, hd], [B, heads, splits, 2]
+    // Only the tensor-core kernel's form for other score rules reads these (attn_decode_mma.cu, WIN):
+    // maps > 1: `heads` counts score maps; map m of a head takes elements [m hd / maps, (m + 1) hd / maps) of a key row
+    //           and its queries are [B, heads, hd / maps].
+    // sigmoid:  the weight of a key is sigmoid(q.k scale + pb[h] - r1[h] ln(1 + r2[h] (i - j))), not normalised (float32
+    //           [heads / maps] each, or null for zero).
+    // out_f32:  results as float32.
+    const float* r1 = nullptr; const float* r2 = nullptr; const float* pb = nullptr;
+    int maps = 1, sigmoid = 0, out_f32 = 0;
 };
 
 // One block per (sequence, head); threads over the head's elements.  A split that saw no

@@ -62,7 +62,9 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_address) {
     return v;
 }
 
-template <int HD, bool FUSED, bool CLUSTER>
+// WIN: other score rules on the same tiles (DecodeArgs: several score maps per head over one key row, sigmoid weights
+// with a logarithmic distance term, float32 results); without FUSED and CLUSTER.
+template <int HD, bool FUSED, bool CLUSTER, bool WIN = false>
 __global__ void __launch_bounds__(THREADS, 2)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                        tiattn::DecodeArgs a, FuseArgs f, int* status) {
@@ -189,21 +191,47 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     // the queries as A fragments: row lane/4 (and +8) is a query head, zero beyond `rows`
     uint32_t qf[KSTEPS][4];
     {
-        const bf16* q = FUSED ? q_s : (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * HD;
+        // (WIN with several maps: a map's query is as long as its share of the key row and stands at that share's place
+        // in a row of zeros, so that the product over the whole row is the map's score)
+        const int qd = WIN ? HD / a.maps : HD;
+        const bf16* q = FUSED ? q_s : (const bf16*)a.q + (size_t)b * a.q_stride + (size_t)h0 * qd;
         const int r0 = lane >> 2, r1 = r0 + 8, c = (lane & 3) * 2;
+        const int off0 = WIN ? ((h0 + r0) % a.maps) * qd : 0, off1 = WIN ? ((h0 + r1) % a.maps) * qd : 0;
+        auto ldq = [&](int r, int off, int d) -> uint32_t {
+            if (r >= rows) return 0u;
+            if (WIN && (d < off || d >= off + qd)) return 0u;
+            return *reinterpret_cast<const uint32_t*>(q + (size_t)r * qd + d - off);
+        };
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
             const int d = ks * 16 + c;
-            qf[ks][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r0 * HD + d) : 0u;
-            qf[ks][1] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r1 * HD + d) : 0u;
-            qf[ks][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r0 * HD + d + 8) : 0u;
-            qf[ks][3] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q + (size_t)r1 * HD + d + 8) : 0u;
+            qf[ks][0] = ldq(r0, off0, d);
+            qf[ks][1] = ldq(r1, off1, d);
+            qf[ks][2] = ldq(r0, off0, d + 8);
+            qf[ks][3] = ldq(r1, off1, d + 8);
+        }
+    }
+    // WIN, sigmoid weights: the two rows' constants; nothing is normalised, so every maximum stands at 0 and every sum at 0
+    const bool sig = WIN && a.sigmoid;
+    float c1[2] = {0.f, 0.f}, c2[2] = {0.f, 0.f}, cb[2] = {0.f, 0.f};
+    if constexpr (WIN) {
+        if (sig) {
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int row = (lane >> 2) + r * 8;
+                if (row < rows) {
+                    const int h = (h0 + row) / a.maps;
+                    if (a.r1) { c1[r] = a.r1[h]; c2[r] = a.r2[h]; }
+                    if (a.pb) cb[r] = a.pb[h];
+                }
+            }
         }
     }
     float o[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // rows lane/4 and lane/4 + 8
+    if (sig) m_run[0] = m_run[1] = 0.f;
 
     // Scores are kept in base-2 units: exp(x * scale - m) = 2^(x * scale * log2(e) - m2), one
     // multiply-add and one ex2 per element.
@@ -269,6 +297,25 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
 #pragma unroll
                 for (int e = 0; e < 4; e++) s[nt][e] += s2[nt][e];
         }
+        float alpha[2] = {1.f, 1.f};
+        uint32_t pf[4];
+        if (sig) {
+            // weights of their own: sigmoid(score + bias - r1 ln(1 + r2 distance)), zero outside [lo, L)
+            float p[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int pos = p0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int r = e >> 1;
+                    const float x = fmaf(s[nt][e], a.scale, cb[r]) - c1[r] * log1pf(c2[r] * (float)(L - 1 - pos));
+                    p[nt][e] = (pos >= lo && pos < L) ? 1.f / (1.f + __expf(-x)) : 0.f;
+                }
+            pf[0] = pack_bf16(p[0][0], p[0][1]);
+            pf[1] = pack_bf16(p[0][2], p[0][3]);
+            pf[2] = pack_bf16(p[1][0], p[1][1]);
+            pf[3] = pack_bf16(p[1][2], p[1][3]);
+        } else {
         // scale, mask, online softmax (rows lane/4 and lane/4 + 8; columns are positions)
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -280,7 +327,6 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
                 s[nt][e] = ok ? s[nt][e] * scale2 : -INFINITY;
                 mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
             }
-        float alpha[2];
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -289,7 +335,6 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             alpha[r] = (m_new > -INFINITY && m_new != m_run[r]) ? ex2(m_run[r] - m_new) : 1.f;
             m_run[r] = m_new;
         }
-        uint32_t pf[4];
         {
             float p[2][4];
 #pragma unroll
@@ -305,6 +350,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             pf[1] = pack_bf16(p[0][2], p[0][3]);
             pf[2] = pack_bf16(p[1][0], p[1][1]);
             pf[3] = pack_bf16(p[1][2], p[1][3]);
+        }
         }
         // O = O * alpha + P V; the rescaling is skipped while no row's maximum moved
         {
@@ -388,7 +434,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             fin_o[idx] = acc;
             if (d == 0) { fin_ml[r * 2] = m; fin_ml[r * 2 + 1] = l; }
         } else if (a.n_splits == 1) {
-            ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+            const float res = sig ? acc : (l > 0.f ? acc / l : 0.f);
+            if (WIN && a.out_f32) ((float*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = res;
+            else ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = __float2bfloat16_rn(res);
         } else {
             const size_t base = ((size_t)b * a.n_heads + h) * a.n_splits + split;
             a.part_o[base * HD + d] = acc;
@@ -572,6 +620,66 @@ extern "C" int ti_attn_decode_mma(const void* q, long long q_stride, const void*
     a.part_o = part_o; a.part_ml = part_ml;
     FuseArgs f = {};
     return head_dim == 64 ? launch<64, false>(a, f, n_seq, mode, stream) : launch<128, false>(a, f, n_seq, mode, stream);
+}
+
+namespace {
+template <int HD>
+int launch_win(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
+    constexpr size_t stage_bytes = 2 * TILE * HD * 2;
+    constexpr size_t merge_bytes = (4 * 16 * HD + 2 * 4 * 16 + 16 * HD + 2 * 16) * sizeof(float);
+    constexpr size_t smem = (STAGES * stage_bytes > merge_bytes ? STAGES * stage_bytes : merge_bytes) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        TI_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel<HD, false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    CUtensorMap km, vm;
+    const long long rows = (long long)a.n_pages * a.n_kv_heads * TILE;
+    if (int rc = page_map(a.k_pages, rows, HD, &km)) return rc;
+    if (int rc = page_map(a.v_pages, rows, HD, &vm)) return rc;
+    int* status = ti_status_ptr();
+    TI_REQUIRE(status != nullptr, "attention_decode: no status word");
+    const int g = a.n_heads / a.n_kv_heads;
+    dim3 grid(n_seq, a.n_kv_heads * ((g + 15) / 16), a.n_splits);
+    FuseArgs f = {};
+    TI_CUDA(ti_launch_class<3>(attn_decode_mma_kernel<HD, false, false, true>, grid, dim3(THREADS), smem, stream, km, vm, a, f, status));
+    TI_CHECK_LAUNCH("attention_decode (tensor cores, score rules)");
+    return 0;
+}
+}  // namespace
+
+// The tensor-core kernel under other score rules, for one new token per sequence: `maps` score maps per head over one key
+// row of `width` elements (64 or 128; a map's queries and keys hold width / maps), values of `width` elements too; with
+// `sigmoid` the weight of key j for query i is sigmoid(q.k scale + pb[h] - r1[h] ln(1 + r2[h] (i - j))) and nothing is
+// normalised, else a softmax per map.  q: [B, heads * maps, width / maps]; out: [B, heads * maps, width], bfloat16 or (out_f32)
+// float32, written here when n_splits == 1; else every split leaves part_o [B, heads * maps, splits, width] and part_ml
+// [B, heads * maps, splits, 2] (maximum and sum; both 0 under sigmoid) for the caller's merge.  bfloat16, pages of 64.
+extern "C" int ti_attn_decode_mma_scored(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                         const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
+                                         const int* seq_slot, const int* seq_len, int n_seq, int n_heads, int n_kv_heads,
+                                         int maps, int width, float scale, int window, int sigmoid, const float* r1,
+                                         const float* r2, const float* pb, int n_splits, void* out, long long o_stride,
+                                         int out_f32, float* part_o, float* part_ml, int dtype, cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(dtype == TI_BF16, "attention_decode (score rules): bfloat16 only");
+    TI_REQUIRE(width == 64 || width == 128, "attention_decode (score rules): rows of %d elements are not 64 or 128", width);
+    TI_REQUIRE(maps >= 1 && width % (8 * maps) == 0, "attention_decode (score rules): %d maps do not share a row of %d", maps, width);
+    TI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "attention_decode: bad head counts");
+    TI_REQUIRE(page_size == TILE, "attention_decode: pages of %d positions, this kernel works on %d", page_size, TILE);
+    TI_REQUIRE(ring_rows % page_size == 0, "attention_decode: ring of %d rows is not whole pages", ring_rows);
+    TI_REQUIRE(window == 0 || ring_rows == 0 || ring_rows >= window, "attention_decode: ring smaller than the window");
+    TI_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: bad split count %d", n_splits);
+    TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
+    TI_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_decode (score rules): the distance term needs both of its constants");
+    TI_REQUIRE((reinterpret_cast<uintptr_t>(q) & 3) == 0 && q_stride % 2 == 0, "attention_decode: queries must be 4-byte aligned");
+    tiattn::DecodeArgs a;
+    a.q = q; a.q_stride = q_stride; a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = page_table;
+    a.table_width = table_width; a.page_size = page_size; a.ring_rows = ring_rows; a.n_pages = n_pages;
+    a.seq_slot = seq_slot; a.seq_len = seq_len; a.n_heads = n_heads * maps; a.n_kv_heads = n_kv_heads; a.hd = width;
+    a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
+    a.part_o = part_o; a.part_ml = part_ml;
+    a.r1 = r1; a.r2 = r2; a.pb = pb; a.maps = maps; a.sigmoid = sigmoid; a.out_f32 = out_f32;
+    return width == 64 ? launch_win<64>(a, n_seq, stream) : launch_win<128>(a, n_seq, stream);
 }
 
 // The same with the step before it folded in: q[B, heads, hd], k and v[B, kv_heads, hd] are the

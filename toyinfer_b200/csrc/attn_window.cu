@@ -612,6 +612,29 @@ extern "C" int ti_attn_window_decode(const void* q, long long q_stride, void* ou
     });
 }
 
+// The merge alone, for partial results that another kernel left (the tensor-core kernel for single tokens): part_o
+// [n_seq, virtual heads, splits, vdim], part_ml [n_seq, virtual heads, splits, 2] -> out [n_seq, virtual heads * vdim].
+extern "C" int ti_attn_window_merge(const float* part_o, const float* part_ml, void* out, long long o_stride, int out_f32, int n_seq,
+                                    int n_virtual, int vdim, int splits, int mode, int dtype, cudaStream_t stream) {
+    if (n_seq == 0) return 0;
+    TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_virtual > 0 && vdim > 0 && splits >= 1 && part_o && part_ml, "attn_window_merge: bad sizes");
+    TI_REQUIRE(mode == 0 || mode == 1, "attn_window_merge: unknown mode %d", mode);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        auto go = [&](auto ot, auto md) -> int {
+            using OT = decltype(ot);
+            TI_CUDA(ti_launch_class<4>(attn_window_merge_kernel<OT, decltype(md)::value>, dim3(n_virtual, n_seq), dim3(64), 0, stream, part_o,
+                                       part_ml, (OT*)out, o_stride, n_virtual, vdim, splits));
+            TI_CHECK_LAUNCH("attn_window_merge");
+            return 0;
+        };
+        auto with_mode = [&](auto ot) -> int {
+            return mode == 1 ? go(ot, std::integral_constant<int, 1>()) : go(ot, std::integral_constant<int, 0>());
+        };
+        return out_f32 ? with_mode(float()) : with_mode(T());
+    });
+}
+
 // a: float32 [M, heads, 2, vdim] (the two maps' outputs); gate: [M, heads] logits of the engine's type with row stride
 // g_stride, or null; out: [M, heads * vdim] with row stride o_stride:  (a1 - lambda a2) / rms(.) * (1 - diff) * sigmoid(gate).
 extern "C" int ti_diff_combine(const float* a, const void* gate, long long g_stride, void* out, long long o_stride, int M, int n_heads,

@@ -111,6 +111,26 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
     pages = _pages(mem, q.dtype, G, maps * dim, vdim, "attention_window")
     out = torch.zeros((M, HV * vdim), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     code = _code(q, "attention_window")
+    if batch.mode == "extend" and tensor_cores and q.dtype == torch.bfloat16 and maps * dim == vdim and vdim in (64, 128) \
+            and dim % 8 == 0 and mem.page_size == 64 and (maps == 1 if mode == "sigmoid" else (r1 is None and pb is None)) \
+            and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0:
+        # single tokens on the tensor-core kernel that the dense model decodes with (csrc/attn_decode_mma.cu): a key row as
+        # long as a value row, shared by the maps; weights are rounded to bfloat16 for the second product
+        from .attention import decode_splits as tile_splits
+        span = min(batch.plan_len, window + mem.page_size) if window > 0 else batch.plan_len
+        splits = tile_splits(M, G, span, mem.page_size, sm_count(q.device), n_live=batch.n_real_seq)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = torch.empty((M, HV, splits, vdim), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((M, HV, splits, 2), dtype=torch.float32, device=q.device)
+        _call(_fn("ti_attn_decode_mma_scored", [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, I, F, I, I, P, P, P, I, P, L, I, P, P, I, P]),
+              _ptr(q), q.stride(0), pages[0], pages[1], pages[2], pages[3], pages[4], 0, pages[5], _ptr(batch.seq_slot),
+              _ptr(batch.seq_len), M, H, G, maps, vdim, float(scale), int(window), MODES[mode], _ptr(r1), _ptr(r2), _ptr(pb), splits,
+              _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(part_o), _ptr(part_ml), code, _stream())
+        if splits > 1:
+            _call(_fn("ti_attn_window_merge", [P, P, P, L, I, I, I, I, I, I, I, P]), _ptr(part_o), _ptr(part_ml), _ptr(out), out.stride(0),
+                  1 if out_f32 else 0, M, HV, vdim, splits, MODES[mode], code, _stream())
+        return out
     if batch.mode == "extend":
         span = min(batch.plan_len, window) if window > 0 else batch.plan_len
         splits = decode_splits(M, HV, heads_per_block(H, G), span, sm_count(q.device))
