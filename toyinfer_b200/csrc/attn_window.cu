@@ -52,9 +52,14 @@ __global__ void attn_window_prepare_kernel(T* __restrict__ qkv, long long ld, co
     extern __shared__ float sm[];       // the row as floats, then 33 for the sums
     const int nq = H * maps * dim, nk = G * maps * dim, nv = G * vdim, N = nq + nk + nv;
     float* red = sm + N;
+    // where the token's keys and values go does not depend on the kernel before this one: the step's positions, slots and
+    // page table were uploaded before its first kernel
+    const int m = blockIdx.x;
+    const int p = tok_pos[m], slot = seq_slot[tok_seq[m]];
+    const int pidx = p / pg.page_size;
+    const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : 0;
     ti_pdl_sync();
     qkv = ti_dependent(qkv);
-    const int m = blockIdx.x;
     T* row = qkv + (size_t)m * ld;
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x; i < N; i += blockDim.x) {
@@ -67,9 +72,6 @@ __global__ void attn_window_prepare_kernel(T* __restrict__ qkv, long long ld, co
     if (q_w) inv_q = rsqrtf(block_sum(sq, red) / (float)nq + eps);
     if (k_w) inv_k = rsqrtf(block_sum(sk, red) / (float)nk + eps);
     __syncthreads();
-    const int p = tok_pos[m], slot = seq_slot[tok_seq[m]];
-    const int pidx = p / pg.page_size;
-    const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : 0;
     const int pp = (page >= 0 && page < pg.n_pages) ? page : 0;       // page 0 is scratch
     const int prow = p % pg.page_size;
     const int half = rot >> 1, kw = maps * dim;
@@ -497,7 +499,7 @@ extern "C" int ti_attn_window_prepare(void* qkv, long long ld, const float* bias
             TI_CUDA(cudaFuncSetAttribute(attn_window_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = smem;
         }
-        TI_CUDA(ti_launch_class<2>(attn_window_prepare_kernel<T>, dim3(M), dim3(N <= 1024 ? 128 : 256), smem, stream, (T*)qkv, ld, bias,
+        TI_CUDA(ti_launch_class<2>(attn_window_prepare_kernel<T>, dim3(M), dim3(N <= 1024 ? 128 : N <= 2048 ? 256 : 512), smem, stream, (T*)qkv, ld, bias,
                                    q_w, k_w, eps, cos_t, sin_t, cos_t ? rot : 0, max_pos, tok_pos, tok_seq, seq_slot, pg, n_heads,
                                    n_kv_heads, maps, dim, vdim));
         TI_CHECK_LAUNCH("attn_window_prepare");

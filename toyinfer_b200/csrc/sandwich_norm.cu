@@ -27,16 +27,18 @@ __global__ void post_norm_add_norm_kernel(float* __restrict__ h, const T* __rest
     const size_t base = (size_t)src * H;
     float inv_y = 0.f;
     if (y) {
+        // the stream's row comes in with the pending output, so that the sum below waits for no second read of memory
         float sy = 0.f;
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             const float v = to_f32(y[base + i]);
+            row[i] = h[base + i];
             sy = fmaf(v, v, sy);
         }
         inv_y = rsqrtf(block_sum(sy, red) / (float)H + eps);
     }
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float x = h[base + i];
+        float x = y ? row[i] : h[base + i];        // (a thread reads back what it wrote itself)
         if (y) x += to_f32(y[base + i]) * inv_y * w_post[(size_t)i * post_stride];
         if (!ok) x = 0.f;
         row[i] = x;

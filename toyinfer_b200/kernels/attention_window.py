@@ -109,7 +109,6 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
         raise KernelError(f"attention_window: unknown mode {mode!r}")
     G = mem.n_kv_heads
     pages = _pages(mem, q.dtype, G, maps * dim, vdim, "attention_window")
-    out = torch.zeros((M, HV * vdim), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     code = _code(q, "attention_window")
     if batch.mode == "extend" and tensor_cores and q.dtype == torch.bfloat16 and maps * dim == vdim and vdim in (64, 128) \
             and dim % 8 == 0 and mem.page_size == 64 and (maps == 1 if mode == "sigmoid" else (r1 is None and pb is None)) \
@@ -119,6 +118,7 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
         from .attention import decode_splits as tile_splits
         span = min(batch.plan_len, window + mem.page_size) if window > 0 else batch.plan_len
         splits = tile_splits(M, G, span, mem.page_size, sm_count(q.device), n_live=batch.n_real_seq)
+        out = torch.empty((M, HV * vdim), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)    # every row is a sequence's
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((M, HV, splits, vdim), dtype=torch.float32, device=q.device)
@@ -131,6 +131,7 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
             _call(_fn("ti_attn_window_merge", [P, P, P, L, I, I, I, I, I, I, I, P]), _ptr(part_o), _ptr(part_ml), _ptr(out), out.stride(0),
                   1 if out_f32 else 0, M, HV, vdim, splits, MODES[mode], code, _stream())
         return out
+    out = torch.zeros((M, HV * vdim), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     if batch.mode == "extend":
         span = min(batch.plan_len, window) if window > 0 else batch.plan_len
         splits = decode_splits(M, HV, heads_per_block(H, G), span, sm_count(q.device))
