@@ -718,10 +718,11 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             q = rnd(B, nh * maps, hd)
             f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
             r1, r2, pb = (f32(nh), f32(nh), -2 * f32(nh)) if kind == "sigmoid" else (None, None, None)
+            tab = KW.distance_table(r1, r2, pb, nh, window, dev) if kind == "sigmoid" else None
             seen = min(ctx, window)
             # the visible keys and values are read once per kv head
             return (lambda: KW.attend(q, maps, vd, mem, hd ** -0.5, window, "sigmoid" if kind == "sigmoid" else "softmax", batch,
-                                      r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid")), \
+                                      r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid", table=tab)), \
                 B * seen * nkv * (maps * hd + vd) * 2, 2.0 * B * seen * nh * maps * (hd + vd)
         if name.startswith("attn_window"):                # attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]]: a whole prompt
             from toyinfer_b200.kernels import attention_window as KW

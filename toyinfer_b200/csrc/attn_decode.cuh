@@ -20,9 +20,11 @@ struct DecodeArgs {
     //           and its queries are [B, heads, hd / maps].
     // sigmoid:  the weight of a key is sigmoid(q.k scale + pb[h] - r1[h] ln(1 + r2[h] (i - j))), not normalised (float32
     //           [heads / maps] each, or null for zero).
+    //           With `table` (float32 [heads / maps, far + 1]) the bias and distance term come from there instead, as
+    //           -log2(e) (pb[h] - r1[h] ln(1 + r2[h] d)) at distance min(d, far).
     // out_f32:  results as float32.
-    const float* r1 = nullptr; const float* r2 = nullptr; const float* pb = nullptr;
-    int maps = 1, sigmoid = 0, out_f32 = 0;
+    const float* r1 = nullptr; const float* r2 = nullptr; const float* pb = nullptr; const float* table = nullptr;
+    int maps = 1, sigmoid = 0, out_f32 = 0, far = 0;
 };
 
 // One block per (sequence, head); threads over the head's elements.  A split that saw no

@@ -214,6 +214,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     // WIN, sigmoid weights: the two rows' constants; nothing is normalised, so every maximum stands at 0 and every sum at 0
     const bool sig = WIN && a.sigmoid;
     float c1[2] = {0.f, 0.f}, c2[2] = {0.f, 0.f}, cb[2] = {0.f, 0.f};
+    const float* trow[2] = {a.table, a.table};       // the rows' lines of the distance table, when there is one
     if constexpr (WIN) {
         if (sig) {
 #pragma unroll
@@ -221,6 +222,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
                 const int row = (lane >> 2) + r * 8;
                 if (row < rows) {
                     const int h = (h0 + row) / a.maps;
+                    if (a.table) trow[r] = a.table + (size_t)h * (a.far + 1);
                     if (a.r1) { c1[r] = a.r1[h]; c2[r] = a.r2[h]; }
                     if (a.pb) cb[r] = a.pb[h];
                 }
@@ -240,6 +242,18 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     for (int i = 0; i < my_n; i++) {
         const int stage = i % STAGES;
         if (t == 0 && i + STAGES - 1 < my_n) issue(i + STAGES - 1);   // its stage was drained in iteration i-1
+        float tb[2][4] = {};
+        if constexpr (WIN) {
+            if (sig && a.table) {       // the table's entries for this thread's scores, on their way while the tile arrives
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int pos = (my_lo + i) * TILE + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        tb[nt][e] = trow[e >> 1][min(max(L - 1 - pos, 0), a.far)];
+                    }
+            }
+        }
         if (!mbar_wait(&full[stage], (uint32_t)((i / STAGES) & 1))) {
             // the data never came: note it, work on whatever the buffer holds (shared memory only)
             // and leave at the barrier below, where every thread sees the flag
@@ -308,8 +322,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
                 for (int e = 0; e < 4; e++) {
                     const int pos = p0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int r = e >> 1;
-                    const float x = fmaf(s[nt][e], a.scale, cb[r]) - c1[r] * log1pf(c2[r] * (float)(L - 1 - pos));
-                    p[nt][e] = (pos >= lo && pos < L) ? 1.f / (1.f + __expf(-x)) : 0.f;
+                    // sigmoid(x) = 1 / (1 + 2^(-x log2(e)))
+                    const float x2 = a.table ? fmaf(s[nt][e], -scale2, tb[nt][e])
+                                             : -1.4426950408889634f * (fmaf(s[nt][e], a.scale, cb[r]) - c1[r] * log1pf(c2[r] * (float)(L - 1 - pos)));
+                    p[nt][e] = (pos >= lo && pos < L) ? __frcp_rn(1.f + ex2(x2)) : 0.f;
                 }
             pf[0] = pack_bf16(p[0][0], p[0][1]);
             pf[1] = pack_bf16(p[0][2], p[0][3]);
@@ -651,14 +667,16 @@ int launch_win(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
 // The tensor-core kernel under other score rules, for one new token per sequence: `maps` score maps per head over one key
 // row of `width` elements (64 or 128; a map's queries and keys hold width / maps), values of `width` elements too; with
 // `sigmoid` the weight of key j for query i is sigmoid(q.k scale + pb[h] - r1[h] ln(1 + r2[h] (i - j))) and nothing is
-// normalised, else a softmax per map.  q: [B, heads * maps, width / maps]; out: [B, heads * maps, width], bfloat16 or (out_f32)
+// normalised (`table`, float32 [heads, far + 1], holds -log2(e) times the bias and distance term per distance up to `far` and
+// is read instead when given), else a softmax per map.  q: [B, heads * maps, width / maps]; out: [B, heads * maps, width], bfloat16 or (out_f32)
 // float32, written here when n_splits == 1; else every split leaves part_o [B, heads * maps, splits, width] and part_ml
 // [B, heads * maps, splits, 2] (maximum and sum; both 0 under sigmoid) for the caller's merge.  bfloat16, pages of 64.
 extern "C" int ti_attn_decode_mma_scored(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                          const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
                                          const int* seq_slot, const int* seq_len, int n_seq, int n_heads, int n_kv_heads,
                                          int maps, int width, float scale, int window, int sigmoid, const float* r1,
-                                         const float* r2, const float* pb, int n_splits, void* out, long long o_stride,
+                                         const float* r2, const float* pb, const float* table, int far, int n_splits, void* out,
+                                         long long o_stride,
                                          int out_f32, float* part_o, float* part_ml, int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (score rules): bfloat16 only");
@@ -671,6 +689,7 @@ extern "C" int ti_attn_decode_mma_scored(const void* q, long long q_stride, cons
     TI_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention_decode: bad split count %d", n_splits);
     TI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split results need scratch memory");
     TI_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_decode (score rules): the distance term needs both of its constants");
+    TI_REQUIRE(far >= 0, "attention_decode (score rules): a distance table of %d lines", far + 1);
     TI_REQUIRE((reinterpret_cast<uintptr_t>(q) & 3) == 0 && q_stride % 2 == 0, "attention_decode: queries must be 4-byte aligned");
     tiattn::DecodeArgs a;
     a.q = q; a.q_stride = q_stride; a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = page_table;
@@ -679,6 +698,7 @@ extern "C" int ti_attn_decode_mma_scored(const void* q, long long q_stride, cons
     a.window = window; a.n_splits = n_splits; a.scale = scale; a.out = out; a.o_stride = o_stride;
     a.part_o = part_o; a.part_ml = part_ml;
     a.r1 = r1; a.r2 = r2; a.pb = pb; a.maps = maps; a.sigmoid = sigmoid; a.out_f32 = out_f32;
+    a.table = sigmoid ? table : nullptr; a.far = far;
     return width == 64 ? launch_win<64>(a, n_seq, stream) : launch_win<128>(a, n_seq, stream);
 }
 

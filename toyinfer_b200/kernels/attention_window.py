@@ -123,9 +123,13 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
         if splits > 1:
             part_o = torch.empty((M, HV, splits, vdim), dtype=torch.float32, device=q.device)
             part_ml = torch.empty((M, HV, splits, 2), dtype=torch.float32, device=q.device)
-        _call(_fn("ti_attn_decode_mma_scored", [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, I, F, I, I, P, P, P, I, P, L, I, P, P, I, P]),
+        use_table = mode == "sigmoid" and table is not None
+        if use_table and (table.dtype != torch.float32 or table.dim() != 2 or table.shape[0] != H or not table.is_contiguous()):
+            raise KernelError("attention_window: the distance table must be dense float32 [heads, far + 1]")
+        _call(_fn("ti_attn_decode_mma_scored", [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, I, F, I, I, P, P, P, P, I, I, P, L, I, P, P, I, P]),
               _ptr(q), q.stride(0), pages[0], pages[1], pages[2], pages[3], pages[4], 0, pages[5], _ptr(batch.seq_slot),
-              _ptr(batch.seq_len), M, H, G, maps, vdim, float(scale), int(window), MODES[mode], _ptr(r1), _ptr(r2), _ptr(pb), splits,
+              _ptr(batch.seq_len), M, H, G, maps, vdim, float(scale), int(window), MODES[mode], _ptr(r1), _ptr(r2), _ptr(pb),
+              _ptr(table) if use_table else None, table.shape[1] - 1 if use_table else 0, splits,
               _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(part_o), _ptr(part_ml), code, _stream())
         if splits > 1:
             _call(_fn("ti_attn_window_merge", [P, P, P, L, I, I, I, I, I, I, I, P]), _ptr(part_o), _ptr(part_ml), _ptr(out), out.stride(0),
