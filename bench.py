@@ -702,6 +702,30 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(1, new, dev), "mixed", [0], [cached], [[0] * new], 1, cached + new)
             return (lambda: K.attention_chunk(q, k, v, mem, 1 / math.sqrt(hd), 0, batch)), \
                 qkv.numel() * 2 + new * nh * hd * 2 + 2 * cached * nkv * hd * 2, 4.0 * nh * hd * new * (cached + (new + 1) / 2)
+        if name.startswith("attn_window_prepare"):        # attn_window_prepare[:TOKENS[,sigmoid|diff]]: biases, norms, rotation, cache store
+            from toyinfer_b200.kernels import attention_window as KW
+            from toyinfer_b200.parts.rope import rotary_tables
+            opts = name.split(":")[1].split(",") if ":" in name else []
+            T = int(opts[0]) if opts else PREFILL_TOKENS
+            kind = opts[1] if len(opts) > 1 else "sigmoid"
+            nh, nkv = 16, 4
+            maps, hd, vd = (1, 128, 128) if kind == "sigmoid" else (2, 64, 128)
+            pages = (T + 63) // 64
+            table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
+            table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
+            mem = KVView(rnd(pages + 1, nkv, 64, maps * hd), rnd(pages + 1, nkv, 64, vd), table, nkv, maps * hd, 0, 0)
+            nq, nk, nv = nh * maps * hd, nkv * maps * hd, nkv * vd
+            qkv = rnd(T, nq + nk + nv)
+            batch = fill_batch(BatchBuffers(1, T, dev), "start", [0], [0], [[0] * T], 1, T)
+            f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
+            bias, qw, kw_ = (f32(nq + nk + nv), f32(nq), f32(nk)) if kind == "sigmoid" else (None, None, None)
+            tables = None
+            if kind != "sigmoid":
+                cos, sin = rotary_tables(hd, 1e6, T + 64)
+                tables = (cos.to(dev), sin.to(dev), hd)
+            # the projection's row read and written back, keys and values written to the pages
+            return (lambda: KW.prepare(qkv, bias, qw, kw_, 1e-6, tables, nh, nkv, maps, hd, vd, mem, batch)), \
+                (2 * (nq + nk + nv) + nk + nv) * T * 2, 0.0
         if name.startswith("attn_window_decode"):         # attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]]: one token per sequence
             from toyinfer_b200.kernels import attention_window as KW
             opts = name.split(":")[1].split(",") if ":" in name else []
@@ -830,7 +854,7 @@ def main() -> int:
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K[,BN,SPLITS], attn_decode[:BATCH,CONTEXT[,HEADS,KV_HEADS]], attn_decode_b64, attn_decode_b1, "
                     "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], "
-                    "attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]], attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]], "
+                    "attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]], attn_window_prepare[:TOKENS[,sigmoid|diff]], attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]], "
                     "ssd_scan[:TOKENS[,SEGMENT]], ssd_decode[:BATCH], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],

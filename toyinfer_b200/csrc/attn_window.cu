@@ -31,6 +31,7 @@
 // diff_combine: o = a1 - lambda a2 of the two maps' outputs, o / rms(o) * (1 - diff) * sigmoid(gate).
 #include "common.cuh"
 
+#include <algorithm>
 #include <type_traits>
 
 namespace {
@@ -102,6 +103,124 @@ __global__ void attn_window_prepare_kernel(T* __restrict__ qkv, long long ld, co
             const T y = from_f32<T>(sm[i]);
             row[i] = y;
             ((T*)pg.v_pages)[(((size_t)pp * G + g) * pg.page_size + prow) * vdim + (j - g * vdim)] = y;
+        }
+    }
+}
+
+// Two sums over the block at once; every thread gets both.  `red` is shared memory for 66 floats.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    a = warp_sum(a); b = warp_sum(b);
+    __syncthreads();        // protects `red` against a previous use
+    if (lane == 0) { red[warp] = a; red[33 + warp] = b; }
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    if (warp == 0) {
+        float ta = lane < nw ? red[lane] : 0.f, tb = lane < nw ? red[33 + lane] : 0.f;
+        ta = warp_sum(ta); tb = warp_sum(tb);
+        if (lane == 0) { red[32] = ta; red[65] = tb; }
+    }
+    __syncthreads();
+    a = red[32]; b = red[65];
+}
+
+// E consecutive floats rounded to T and written by one 16-byte store (E * sizeof(T) == 16)
+template <typename T, int E>
+__device__ __forceinline__ void store_run16(T* __restrict__ p, const float (&x)[E]) {
+    static_assert(E * sizeof(T) == 16, "one 16-byte store");
+    T raw[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) raw[e] = from_f32<T>(x[e]);
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(raw);
+}
+
+// The same work on runs of 16 bytes: every size that decides where a run lies (dim, vdim, the row stride) is a multiple of
+// a run's E elements and every pointer is 16-byte aligned, so a run stays within one head and one map.
+template <typename T>
+__global__ void attn_window_prepare_vec_kernel(T* __restrict__ qkv, long long ld, const float* __restrict__ bias,
+                                               const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int max_pos,
+                                               const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                               const int* __restrict__ seq_slot, Pages pg, int H, int G, int maps, int dim, int vdim) {
+    ti_pdl_trigger();
+    constexpr int E = 16 / (int)sizeof(T);
+    extern __shared__ __align__(16) float sm[];       // the row as floats, then 66 for the sums
+    const int nq = H * maps * dim, nk = G * maps * dim, nv = G * vdim, N = nq + nk + nv;
+    float* red = sm + N;
+    const int m = blockIdx.x;
+    const int p = tok_pos[m], slot = seq_slot[tok_seq[m]];
+    const int pidx = p / pg.page_size;
+    const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : 0;
+    ti_pdl_sync();
+    qkv = ti_dependent(qkv);
+    T* row = qkv + (size_t)m * ld;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x * E; i < N; i += blockDim.x * E) {
+        float x[E];
+        T raw[E];
+        *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(row + i);
+#pragma unroll
+        for (int e = 0; e < E; e++) x[e] = to_f32(raw[e]);
+        if (bias) {
+#pragma unroll
+            for (int e = 0; e < E; e += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(bias + i + e);
+                x[e] += b4.x; x[e + 1] += b4.y; x[e + 2] += b4.z; x[e + 3] += b4.w;
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; e += 4) {
+            *reinterpret_cast<float4*>(sm + i + e) = make_float4(x[e], x[e + 1], x[e + 2], x[e + 3]);
+            ss += x[e] * x[e] + x[e + 1] * x[e + 1] + x[e + 2] * x[e + 2] + x[e + 3] * x[e + 3];
+        }
+        if (i < nq) sq += ss;
+        else if (i < nq + nk) sk += ss;
+    }
+    block_sum2(sq, sk, red);        // (its last barrier also makes the whole row visible)
+    const float inv_q = q_w ? rsqrtf(sq / (float)nq + eps) : 1.f, inv_k = k_w ? rsqrtf(sk / (float)nk + eps) : 1.f;
+    const int pp = (page >= 0 && page < pg.n_pages) ? page : 0;       // page 0 is scratch
+    const int prow = p % pg.page_size;
+    const int half = rot >> 1, kw = maps * dim;
+    const float* cs = cos_t ? cos_t + (size_t)min(p, max_pos - 1) * half : nullptr;
+    const float* sn = sin_t ? sin_t + (size_t)min(p, max_pos - 1) * half : nullptr;
+    for (int i = threadIdx.x * E; i < N; i += blockDim.x * E) {
+        float x[E];
+#pragma unroll
+        for (int e = 0; e < E; e += 4) {
+            const float4 v4 = *reinterpret_cast<const float4*>(sm + i + e);
+            x[e] = v4.x; x[e + 1] = v4.y; x[e + 2] = v4.z; x[e + 3] = v4.w;
+        }
+        if (i < nq + nk) {
+            const bool is_q = i < nq;
+            const int seg = is_q ? 0 : nq, j = i - seg, e0 = j % dim;
+            const float* w = is_q ? q_w : k_w;
+            const float inv = is_q ? inv_q : inv_k;
+            if (w) {
+#pragma unroll
+                for (int e = 0; e < E; e++) x[e] = x[e] * inv * w[j + e];
+            }
+            if (cs && e0 < rot) {
+#pragma unroll
+                for (int e = 0; e < E; e++) {
+                    const int el = e0 + e;
+                    if (el < rot) {
+                        const int jo = el < half ? j + e + half : j + e - half;      // the other element of the pair
+                        float o = sm[seg + jo];
+                        if (w) o = o * inv * w[jo];
+                        x[e] = el < half ? x[e] * cs[el] - o * sn[el] : x[e] * cs[el - half] + o * sn[el - half];
+                    }
+                }
+            }
+            store_run16<T, E>(row + i, x);      // keys and values go back too: the tensor-core kernel reads the step's own from the row
+            if (!is_q) {
+                const int g = j / kw;
+                store_run16<T, E>((T*)pg.k_pages + (((size_t)pp * G + g) * pg.page_size + prow) * kw + (j - g * kw), x);
+            }
+        } else {
+            const int j = i - nq - nk, g = j / vdim;
+            store_run16<T, E>(row + i, x);
+            store_run16<T, E>((T*)pg.v_pages + (((size_t)pp * G + g) * pg.page_size + prow) * vdim + (j - g * vdim), x);
         }
     }
 }
@@ -490,7 +609,7 @@ extern "C" int ti_attn_window_prepare(void* qkv, long long ld, const float* bias
     if (check_pages("attn_window_prepare", k_pages, v_pages, page_table, table_width, page_size, n_pages)) return 1;
     Pages pg{k_pages, v_pages, page_table, table_width, page_size, n_pages};
     const long long N = (long long)n_heads * maps * dim + (long long)n_kv_heads * (maps * dim + vdim);
-    const size_t smem = (size_t)(N + 33) * sizeof(float);
+    const size_t smem = (size_t)(N + 66) * sizeof(float);
     TI_REQUIRE(smem <= 200 * 1024, "attn_window_prepare: a projection row of %lld elements does not fit shared memory", N);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
@@ -498,6 +617,23 @@ extern "C" int ti_attn_window_prepare(void* qkv, long long ld, const float* bias
         if (smem > 48 * 1024 && smem > configured) {
             TI_CUDA(cudaFuncSetAttribute(attn_window_prepare_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             configured = smem;
+        }
+        constexpr int E = 16 / (int)sizeof(T);
+        auto a16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+        if (dim % E == 0 && vdim % E == 0 && ld % E == 0 && a16(qkv) && a16(bias) && a16(q_w) && a16(k_w) && a16(k_pages) && a16(v_pages)) {
+            static size_t configured_vec = 0;
+            if (smem > 48 * 1024 && smem > configured_vec) {
+                TI_CUDA(cudaFuncSetAttribute(attn_window_prepare_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                configured_vec = smem;
+            }
+            // a run a thread when the tokens are few (the step is a chain of latencies), two when they fill the device
+            // several times over (more blocks at once)
+            const long long runs = (N / E + (M >= 592 ? 1 : 0)) / (M >= 592 ? 2 : 1);
+            TI_CUDA(ti_launch_class<2>(attn_window_prepare_vec_kernel<T>, dim3(M), dim3((unsigned)std::min<long long>(512, (runs + 31) / 32 * 32)), smem, stream,
+                                       (T*)qkv, ld, bias, q_w, k_w, eps, cos_t, sin_t, cos_t ? rot : 0, max_pos, tok_pos, tok_seq, seq_slot, pg,
+                                       n_heads, n_kv_heads, maps, dim, vdim));
+            TI_CHECK_LAUNCH("attn_window_prepare (16-byte runs)");
+            return 0;
         }
         TI_CUDA(ti_launch_class<2>(attn_window_prepare_kernel<T>, dim3(M), dim3(N <= 1024 ? 128 : N <= 2048 ? 256 : 512), smem, stream, (T*)qkv, ld, bias,
                                    q_w, k_w, eps, cos_t, sin_t, cos_t ? rot : 0, max_pos, tok_pos, tok_seq, seq_slot, pg, n_heads,
