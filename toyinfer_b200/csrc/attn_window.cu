@@ -18,7 +18,8 @@
 //   projections' biases, norms ALL of q's and ALL of k's elements at once (x * rsqrt(mean(x^2) + eps)
 //   * w[i], a weight per element; each optional), rotates the first `rot` elements of every map of
 //   q and k by the token's position (pairs (e, e + rot/2), tables of cos and sin), writes q, k and
-//   v back in place and stores k and v at the token's position in the sequence's pages.
+//   v back in place and stores k and v at the token's position in the sequence's pages.  Where the
+//   sizes and addresses allow it the row moves in runs of 16 bytes (attn_window_prepare_vec).
 // attn_window: any number of new tokens per sequence after any number of cached ones; all keys
 //   are read from the pages, so the step's own must be stored first.  Grid (query tiles of 32,
 //   virtual heads, sequences), 128 threads: thread t works on query row t / 4; its 4 threads split
@@ -27,7 +28,8 @@
 // attn_window_decode: one query per sequence; a block takes up to four virtual heads of one kv
 //   head and one map, and one of `splits` ranges of the window's keys; a warp 32 keys at a time (a
 //   lane a key for the scores, then the lanes the value's elements); ranges are merged by a second
-//   kernel when there are several.
+//   kernel when there are several (ti_attn_window_merge serves the tensor-core decode kernel of
+//   attn_decode_mma.cu the same way, which takes bfloat16 single tokens where it can).
 // diff_combine: o = a1 - lambda a2 of the two maps' outputs, o / rms(o) * (1 - diff) * sigmoid(gate).
 #include "common.cuh"
 

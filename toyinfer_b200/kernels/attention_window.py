@@ -96,7 +96,10 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
     the score under the sigmoid.  mode: "softmax" or "sigmoid" (weights not normalised over the keys).
     k [M, kv_heads * maps * dim], v [M, kv_heads * vdim]: the step's own keys and values as ``prepare`` left them, and
     ``table`` (``distance_table``; sigmoid mode) let prompts and pieces run on the tensor cores: bfloat16, keys and values
-    of 64 or 128 elements each (csrc/attn_prefill_tc.cu); weights are then rounded to bfloat16 for the second product."""
+    of 64 or 128 elements each (csrc/attn_prefill_tc.cu); weights are then rounded to bfloat16 for the second product.
+    Single tokens (a step in which every sequence goes on by one) run on the tensor-core decode kernel
+    (csrc/attn_decode_mma.cu) in bfloat16 where a key row, all maps together, is as long as a value row (64 or 128), with
+    the same rounding of the weights; else on the CUDA-core kernel of csrc/attn_window.cu."""
     _need_cuda(q, r1, r2, pb, what="attention_window")
     M, HV, dim = q.shape
     if HV % maps or q.stride(2) != 1 or q.stride(1) != dim:
