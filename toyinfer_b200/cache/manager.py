@@ -17,7 +17,9 @@ step points there and what it writes is never read.
 Fixed-size states live in one tensor per entry, [slots + 1, *shape], and are zeroed
 when a slot is handed out (a linear-attention mixer keeps its [heads, dim, vdim] state there).
 A request with ``values=False`` gets rows without a second array beside them (a latent that
-serves as key and value at once).
+serves as key and value at once).  An entry whose mixer is several mixers side by side asks
+with a tuple of requests and gets a tuple of views in the same order (keys and values for
+one of them, a state for another); each member is placed as an entry's single request would be.
 
 The reference keeps one sequence's keys and values as [layers, max_seq_len, kv_dim]
 (src/transformer.cpp:188-195) and the position in a host variable
@@ -118,12 +120,19 @@ class _KVGroup:
                       self.req.head_dim, self.req.window, self.ring_rows)
 
 
+def _members(req) -> tuple:
+    """The single requests of what an entry asks for (a request, a tuple of them, or None)."""
+    if req is None:
+        return ()
+    return tuple(req) if isinstance(req, (tuple, list)) else (req,)
+
+
 def bytes_per_token(requests: Sequence[Any], dtype: torch.dtype) -> int:
     """Bytes of cache that one position of one sequence takes, over all schedule entries' requests
     (keys and values; fixed-size states do not grow with the length and count nothing here)."""
     elem = torch.empty((), dtype=dtype).element_size()
     return sum((r.head_dim + ((r.value_dim or r.head_dim) if r.values else 0)) * r.n_kv_heads * elem
-               for r in requests if isinstance(r, KVRequest))
+               for req in requests for r in _members(req) if isinstance(r, KVRequest))
 
 
 class CacheManager:
@@ -140,18 +149,24 @@ class CacheManager:
         self.slots = SlotAllocator(self.n_slots)
         self.length: Dict[int, int] = {}
         self.kv_groups: List[_KVGroup] = []
-        self.states: Dict[int, torch.Tensor] = {}
-        by_key: Dict[KVRequest, List[int]] = {}
-        for entry, req in enumerate(requests):
-            if req is None:
+        self.states: Dict[Any, torch.Tensor] = {}
+        by_key: Dict[KVRequest, List[Any]] = {}
+        several: Dict[int, List[Any]] = {}          # entries that asked with a tuple: the keys of their members, in order
+        for entry, asked in enumerate(requests):
+            if asked is None:
                 continue
-            if isinstance(req, KVRequest):
-                by_key.setdefault(req, []).append(entry)
-            elif isinstance(req, StateRequest):
-                self.states[entry] = torch.zeros((self.n_slots + 1,) + tuple(req.shape),
-                                                 dtype=req.dtype, device=device)
-            else:
-                raise CacheError(f"schedule entry {entry} asks for memory of unknown kind {type(req).__name__}")
+            tupled = isinstance(asked, (tuple, list))
+            for i, req in enumerate(_members(asked)):
+                key = (entry, i) if tupled else entry
+                if tupled:
+                    several.setdefault(entry, []).append(key)
+                if isinstance(req, KVRequest):
+                    by_key.setdefault(req, []).append(key)
+                elif isinstance(req, StateRequest):
+                    self.states[key] = torch.zeros((self.n_slots + 1,) + tuple(req.shape),
+                                                   dtype=req.dtype, device=device)
+                else:
+                    raise CacheError(f"schedule entry {entry} asks for memory of unknown kind {type(req).__name__}")
         for req, entries in by_key.items():
             self.kv_groups.append(_KVGroup(req, entries, self.n_slots, self.max_tokens,
                                            self.max_seq_len, dtype, device))
@@ -161,6 +176,8 @@ class CacheManager:
                 self._views[e] = g.view(e)
         for e, t in self.states.items():
             self._views[e] = StateView(t)
+        for entry, keys in several.items():
+            self._views[entry] = tuple(self._views.pop(k) for k in keys)
 
     # -- slots ----------------------------------------------------------------
     def allocate_slot(self) -> int:

@@ -9,7 +9,9 @@
 // map * dim of that head's row, and the head's value.
 //
 // For the query at position i and the key at position j of a sequence, visible when
-// 0 <= i - j < window (window <= 0: every j <= i):
+// 0 <= i - j < window (window <= 0: every j <= i), or, whatever the window, when j <= i and
+// j < keep_first (a sequence's first positions stay visible to every later query, at their own
+// positions); results may be multiplied by `out_scale` before they are rounded:
 //     s_ij = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))          (r1 == null: no distance term)
 //     MODE 0:  softmax over the visible j,  o_i = sum_j p_ij v_j
 //     MODE 1:  w_ij = sigmoid(s_ij + pb[h]), not normalised over j,  o_i = sum_j w_ij v_j
@@ -20,6 +22,11 @@
 //   q and k by the token's position (pairs (e, e + rot/2), tables of cos and sin), writes q, k and
 //   v back in place and stores k and v at the token's position in the sequence's pages.  Where the
 //   sizes and addresses allow it the row moves in runs of 16 bytes (attn_window_prepare_vec).
+// attn_head_prepare: the same place in a step for a design whose norms run per head: a warp per
+//   token and head over the projection's row [q | k | v | ...] (one map): adds the projections'
+//   biases, norms every head of q and of k over its own `dim` elements with one weight [dim] for all
+//   heads (each optional), rotates the first `rot` elements of every head of q and k, pairing either
+//   (e, e + rot/2) or neighbours (2e, 2e + 1) with the same tables, writes back and stores k and v.
 // attn_window: any number of new tokens per sequence after any number of cached ones; all keys
 //   are read from the pages, so the step's own must be stored first.  Grid (query tiles of 32,
 //   virtual heads, sequences), 128 threads: thread t works on query row t / 4; its 4 threads split
@@ -227,6 +234,68 @@ __global__ void attn_window_prepare_vec_kernel(T* __restrict__ qkv, long long ld
     }
 }
 
+// A warp per (token, head): the heads of a token's row are its n_heads queries, then n_kv_heads keys, then n_kv_heads values.
+// Shared memory: a head's elements per warp.  pairing 0: element e < rot/2 turns with e + rot/2; 1: element 2e with 2e + 1.
+template <typename T>
+__global__ void attn_head_prepare_kernel(T* __restrict__ qkv, long long ld, const float* __restrict__ bias,
+                                         const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int pairing,
+                                         int max_pos, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                         const int* __restrict__ seq_slot, Pages pg, long long rows, int H, int G, int dim, int vdim,
+                                         int width) {
+    ti_pdl_trigger();
+    extern __shared__ float sm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (r >= rows) return;                                  // (warps never meet at a block-wide barrier)
+    float* x = sm + (size_t)warp * width;
+    const int per = H + 2 * G;
+    const long long m = r / per;
+    const int j = (int)(r - m * per);
+    const int kind = j < H ? 0 : j < H + G ? 1 : 2;         // query, key, value
+    const int head = kind == 0 ? j : kind == 1 ? j - H : j - H - G;
+    const int n = kind == 2 ? vdim : dim;
+    const int off = kind == 0 ? head * dim : kind == 1 ? H * dim + head * dim : (H + G) * dim + head * vdim;
+    // where the token's keys and values go does not depend on the kernel before this one
+    const int p = tok_pos[m], slot = seq_slot[tok_seq[m]];
+    const int pidx = p / pg.page_size;
+    const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : 0;
+    ti_pdl_sync();
+    qkv = ti_dependent(qkv);
+    T* row = qkv + (size_t)m * ld + off;
+    float ss = 0.f;
+    for (int i = lane; i < n; i += 32) {
+        const float v = to_f32(row[i]) + (bias ? bias[off + i] : 0.f);
+        x[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float* w = kind == 0 ? q_w : kind == 1 ? k_w : nullptr;
+    if (w) {
+        const float inv = rsqrtf(warp_sum(ss) / (float)n + eps);
+        for (int i = lane; i < n; i += 32) x[i] = x[i] * inv * w[i];
+    }
+    __syncwarp();
+    const int pp = (page >= 0 && page < pg.n_pages) ? page : 0;       // page 0 is scratch
+    const size_t at = ((size_t)pp * G + head) * pg.page_size + p % pg.page_size;
+    T* cache = kind == 1 ? (T*)pg.k_pages + at * dim : kind == 2 ? (T*)pg.v_pages + at * vdim : nullptr;
+    const bool turns = cos_t && kind != 2;
+    const int half = rot >> 1;
+    const float* cs = cos_t ? cos_t + (size_t)min(p, max_pos - 1) * half : nullptr;
+    const float* sn = sin_t ? sin_t + (size_t)min(p, max_pos - 1) * half : nullptr;
+    for (int i = lane; i < n; i += 32) {
+        float v = x[i];
+        if (turns && i < rot) {
+            const bool first = pairing ? !(i & 1) : i < half;
+            const int e = pairing ? i >> 1 : (first ? i : i - half);
+            const float o = x[pairing ? i ^ 1 : (first ? i + half : i - half)];
+            v = first ? v * cs[e] - o * sn[e] : v * cs[e] + o * sn[e];
+        }
+        const T y = from_f32<T>(v);
+        row[i] = y;
+        if (cache) cache[i] = y;
+    }
+}
+
 constexpr int BQ = 32, BKV = 32, THREADS = 128;
 
 template <typename T, typename OT, int MAXC, int MODE>
@@ -234,7 +303,8 @@ __global__ void __launch_bounds__(THREADS)
 attn_window_kernel(const T* __restrict__ q, long long q_stride, OT* __restrict__ out, long long o_stride,
                    const int* __restrict__ cu_new, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                    Pages pg, const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ pb,
-                   int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale, int window) {
+                   int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale, int window, int keep_first,
+                   float out_scale) {
     ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
@@ -268,7 +338,12 @@ attn_window_kernel(const T* __restrict__ q, long long q_stride, OT* __restrict__
     const int nc = (vdim + 3) >> 2;     // value elements per thread (c4, c4 + 4, ...)
     const int last_q = start + min(q0 + BQ, n) - 1;
     const int first_k = window > 0 ? max(0, start + q0 - (window - 1)) : 0;
-    for (int k0 = (first_k / BKV) * BKV; k0 <= last_q; k0 += BKV) {
+    // key tiles: those of the kept first positions that lie before the window's first tile, then the window's own
+    const int k_band = (first_k / BKV) * BKV;
+    const int keep_tiles = (min(keep_first, k_band) + BKV - 1) / BKV;
+    const int n_tiles = keep_tiles + (last_q - k_band) / BKV + 1;
+    for (int it = 0; it < n_tiles; it++) {
+        const int k0 = it < keep_tiles ? it * BKV : k_band + (it - keep_tiles) * BKV;
         __syncthreads();  // previous tile fully consumed (and Qs written, first time)
         for (int rr = t >> 3; rr < BKV; rr += THREADS >> 3) {
             const int p = k0 + rr;
@@ -300,7 +375,7 @@ attn_window_kernel(const T* __restrict__ q, long long q_stride, OT* __restrict__
 #pragma unroll
         for (int c = 0; c < 8; c++) {
             const int kj = k0 + c4 + 4 * c;
-            okc[c] = kj <= qi && kj < end && (window <= 0 || qi - kj < window);
+            okc[c] = kj <= qi && kj < end && (window <= 0 || qi - kj < window || kj < keep_first);
             float x = s[c] * scale;
             if (r1 && okc[c]) x -= a1 * log1pf(a2 * (float)(qi - kj));
             s[c] = x;
@@ -349,8 +424,8 @@ attn_window_kernel(const T* __restrict__ q, long long q_stride, OT* __restrict__
         }
     }
     if (qi < end) {
-        float inv = 1.f;
-        if constexpr (MODE == 0) inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        float inv = out_scale;
+        if constexpr (MODE == 0) inv = l_run > 0.f ? out_scale / l_run : 0.f;
         OT* orow = out + (size_t)(tok0 + qi - start) * o_stride + (size_t)hv * vdim;
 #pragma unroll
         for (int c = 0; c < MAXC; c++)
@@ -384,8 +459,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_window_decode_kernel(const T* __restrict__ q, long long q_stride, OT* __restrict__ out, long long o_stride,
                           const int* __restrict__ seq_len, const int* __restrict__ seq_slot, Pages pg,
                           const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ pb,
-                          int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale, int window, int splits,
-                          float* __restrict__ part_o, float* __restrict__ part_ml) {
+                          int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale, int window, int keep_first,
+                          float out_scale, int splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
     ti_pdl_trigger();
     extern __shared__ __align__(16) float dsm[];         // q: [GH][dim]; o: [DEC_WARPS][GH][32 * VPL]; m, l: [DEC_WARPS][GH][2]
     float* q_sh = dsm;
@@ -403,8 +478,12 @@ attn_window_decode_kernel(const T* __restrict__ q, long long q_stride, OT* __res
     const int lo = window > 0 ? max(0, len - window) : 0;           // first visible key
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t_first = lo / 32, tiles = (len + 31) / 32;
-    const int per = (tiles - t_first + splits - 1) / splits;         // ranges of whole tiles of 32 keys
-    const int t_lo = t_first + sp * per, t_hi = min(tiles, t_lo + per);
+    // tiles of 32 keys in the order they are shared out: those of the kept first positions that lie before the window's
+    // first tile, then the window's own
+    const int keep_tiles = min((keep_first + 31) / 32, t_first);
+    const int n_tiles = keep_tiles + tiles - t_first;
+    const int per = (n_tiles + splits - 1) / splits;
+    const int t_lo = sp * per, t_hi = min(n_tiles, t_lo + per);
     for (int i = threadIdx.x; i < GH * dim; i += DEC_WARPS * 32) {
         const int g = i / dim, d = i - g * dim;
         q_sh[i] = to_f32(q[(size_t)b * q_stride + (size_t)((h0 + g) * maps + map) * dim + d]) * scale;
@@ -421,10 +500,11 @@ attn_window_decode_kernel(const T* __restrict__ q, long long q_stride, OT* __res
 #pragma unroll
         for (int e = 0; e < VPL; e++) acc[g][e] = 0.f;
     }
-    for (int t = t_lo + warp; t < t_hi; t += DEC_WARPS) {
+    for (int vt = t_lo + warp; vt < t_hi; vt += DEC_WARPS) {
+        const int t = vt < keep_tiles ? vt : t_first + vt - keep_tiles;
         const int j = t * 32 + lane;
         int at = -1;                                     // the key's row among all rows of the pages
-        if (j < len && j >= lo) {
+        if (j < len && (j >= lo || j < keep_first)) {
             const int pidx = j / pg.page_size;
             const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : -1;
             if (page >= 0 && page < pg.n_pages) at = (page * n_kv_heads + kvh) * pg.page_size + j % pg.page_size;
@@ -523,7 +603,7 @@ attn_window_decode_kernel(const T* __restrict__ q, long long q_stride, OT* __res
             for (int w = 0; w < DEC_WARPS; w++) o = fmaf(o_sh[(w * GH + g) * 32 * VPL + d], f[w], o);
             if (splits == 1) {
                 if constexpr (MODE == 0) o = l_all > 0.f ? o / l_all : 0.f;
-                out[(size_t)b * o_stride + (size_t)hv * vdim + d] = from_f32<OT>(o);
+                out[(size_t)b * o_stride + (size_t)hv * vdim + d] = from_f32<OT>(o * out_scale);
             } else {
                 part_o[(((size_t)b * n_heads * maps + hv) * splits + sp) * vdim + d] = o;
             }
@@ -537,7 +617,7 @@ attn_window_decode_kernel(const T* __restrict__ q, long long q_stride, OT* __res
 
 template <typename OT, int MODE>
 __global__ void attn_window_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, OT* __restrict__ out,
-                                         long long o_stride, int n_virtual, int vdim, int splits) {
+                                         long long o_stride, int n_virtual, int vdim, int splits, float out_scale) {
     ti_pdl_trigger();
     ti_pdl_sync();
     part_o = ti_dependent(part_o); part_ml = ti_dependent(part_ml);
@@ -548,7 +628,7 @@ __global__ void attn_window_merge_kernel(const float* __restrict__ part_o, const
         for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
             float o = 0.f;
             for (int s = 0; s < splits; s++) o += po[(size_t)s * vdim + d];
-            out[(size_t)b * o_stride + (size_t)hv * vdim + d] = from_f32<OT>(o);
+            out[(size_t)b * o_stride + (size_t)hv * vdim + d] = from_f32<OT>(o * out_scale);
         }
         return;
     }
@@ -560,7 +640,7 @@ __global__ void attn_window_merge_kernel(const float* __restrict__ part_o, const
         float o = 0.f;
         for (int s = 0; s < splits; s++)
             if (ml[2 * s] > -INFINITY) o = fmaf(po[(size_t)s * vdim + d], expf(ml[2 * s] - m_all), o);
-        out[(size_t)b * o_stride + (size_t)hv * vdim + d] = from_f32<OT>(l_all > 0.f ? o / l_all : 0.f);
+        out[(size_t)b * o_stride + (size_t)hv * vdim + d] = from_f32<OT>(l_all > 0.f ? o / l_all * out_scale : 0.f);
     }
 }
 
@@ -645,18 +725,48 @@ extern "C" int ti_attn_window_prepare(void* qkv, long long ld, const float* bias
     });
 }
 
+// qkv: [M, >= heads * dim + kv_heads * (dim + vdim)] of the engine's type, row stride ld (columns after q, k, v are left
+// alone); bias: float32 of q, k and v's length or null; q_w, k_w: float32 [dim] or null (one weight for all heads); cos_t,
+// sin_t: float32 [max_pos, rot / 2] or null; pairing 0: elements (e, e + rot / 2) turn together, 1: (2e, 2e + 1).
+extern "C" int ti_attn_head_prepare(void* qkv, long long ld, const float* bias, const float* q_w, const float* k_w, float eps,
+                                    const float* cos_t, const float* sin_t, int rot, int pairing, int max_pos, const int* tok_pos,
+                                    const int* tok_seq, const int* seq_slot, void* k_pages, void* v_pages, const int* page_table,
+                                    int table_width, int page_size, int n_pages, int M, int n_heads, int n_kv_heads, int dim,
+                                    int vdim, int dtype, cudaStream_t stream) {
+    if (M == 0) return 0;
+    TI_REQUIRE(M > 0 && n_heads > 0 && n_kv_heads > 0 && dim > 0 && vdim > 0, "attn_head_prepare: bad sizes");
+    TI_REQUIRE(!cos_t || (sin_t && rot > 0 && rot % 2 == 0 && rot <= dim && max_pos > 0 && (pairing == 0 || pairing == 1)),
+               "attn_head_prepare: a rotation of %d of %d elements with tables of %d positions", rot, dim, max_pos);
+    if (check_pages("attn_head_prepare", k_pages, v_pages, page_table, table_width, page_size, n_pages)) return 1;
+    Pages pg{k_pages, v_pages, page_table, table_width, page_size, n_pages};
+    const int width = std::max(dim, vdim), warps = 4;
+    const size_t smem = (size_t)warps * width * sizeof(float);
+    TI_REQUIRE(smem <= 48 * 1024, "attn_head_prepare: heads of %d elements are not supported", width);
+    const long long rows = (long long)M * (n_heads + 2 * n_kv_heads);
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<2>(attn_head_prepare_kernel<T>, dim3((unsigned)((rows + warps - 1) / warps)), dim3(warps * 32), smem, stream,
+                                   (T*)qkv, ld, bias, q_w, k_w, eps, cos_t, sin_t, cos_t ? rot : 0, pairing, max_pos, tok_pos, tok_seq,
+                                   seq_slot, pg, rows, n_heads, n_kv_heads, dim, vdim, width));
+        TI_CHECK_LAUNCH("attn_head_prepare");
+        return 0;
+    });
+}
+
 // q: [M, heads * maps, dim] (row stride q_stride); out: [M, heads * maps, vdim] (row stride o_stride), float32 when
 // out_f32 else the engine's type; r1, r2, pb: float32 [heads] or null; mode 0 softmax, 1 sigmoid; window <= 0: all keys.
 extern "C" int ti_attn_window(const void* q, long long q_stride, void* out, long long o_stride, int out_f32, const int* cu_new,
                               const int* seq_start, const int* seq_slot, int n_seq, int max_new, const void* k_pages,
                               const void* v_pages, const int* page_table, int table_width, int page_size, int n_pages,
                               const float* r1, const float* r2, const float* pb, int n_heads, int n_kv_heads, int maps, int dim,
-                              int vdim, float scale, int window, int mode, int dtype, cudaStream_t stream) {
+                              int vdim, float scale, int window, int keep_first, float out_scale, int mode, int dtype,
+                              cudaStream_t stream) {
     if (n_seq == 0 || max_new == 0) return 0;
     TI_REQUIRE(n_seq > 0 && max_new > 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && maps > 0, "attn_window: bad sizes");
     TI_REQUIRE(dim >= 1 && dim <= 256 && vdim >= 1 && vdim <= 256, "attn_window: heads of %d and %d elements are not supported (up to 256)", dim, vdim);
     TI_REQUIRE(n_seq <= 65535 && n_heads * maps <= 65535, "attn_window: too many sequences or heads for one launch");
     TI_REQUIRE(mode == 0 || mode == 1, "attn_window: unknown mode %d", mode);
+    TI_REQUIRE(keep_first >= 0, "attn_window: %d kept first positions", keep_first);
     TI_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attn_window: the distance term needs both of its constants");
     if (check_pages("attn_window", k_pages, v_pages, page_table, table_width, page_size, n_pages)) return 1;
     Pages pg{k_pages, v_pages, page_table, table_width, page_size, n_pages};
@@ -673,7 +783,8 @@ extern "C" int ti_attn_window(const void* q, long long q_stride, void* out, long
                 configured = smem;
             }
             TI_CUDA(ti_launch(attn_window_kernel<T, OT, MAXC, MODE>, grid, dim3(THREADS), smem, stream, (const T*)q, q_stride, (OT*)out,
-                              o_stride, cu_new, seq_start, seq_slot, pg, r1, r2, pb, n_heads, n_kv_heads, maps, dim, vdim, scale, window));
+                              o_stride, cu_new, seq_start, seq_slot, pg, r1, r2, pb, n_heads, n_kv_heads, maps, dim, vdim, scale, window,
+                              window > 0 ? keep_first : 0, out_scale));
             TI_CHECK_LAUNCH("attn_window");
             return 0;
         };
@@ -695,8 +806,8 @@ extern "C" int ti_attn_window_decode(const void* q, long long q_stride, void* ou
                                      const int* seq_len, const int* seq_slot, int n_seq, const void* k_pages, const void* v_pages,
                                      const int* page_table, int table_width, int page_size, int n_pages, const float* r1,
                                      const float* r2, const float* pb, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
-                                     float scale, int window, int mode, int splits, float* part_o, float* part_ml, int dtype,
-                                     cudaStream_t stream) {
+                                     float scale, int window, int keep_first, float out_scale, int mode, int splits, float* part_o,
+                                     float* part_ml, int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(n_seq > 0 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && maps > 0 && splits >= 1, "attn_window_decode: bad sizes");
     TI_REQUIRE(dim >= 1 && dim <= 32 * DEC_MAXE && vdim >= 1 && vdim <= 32 * DEC_MAXE,
@@ -704,6 +815,7 @@ extern "C" int ti_attn_window_decode(const void* q, long long q_stride, void* ou
     TI_REQUIRE(n_seq <= 65535 && n_heads * maps <= 65535, "attn_window_decode: too many sequences or heads for one launch");
     TI_REQUIRE(splits == 1 || (part_o && part_ml), "attn_window_decode: split keys need scratch");
     TI_REQUIRE(mode == 0 || mode == 1, "attn_window_decode: unknown mode %d", mode);
+    TI_REQUIRE(keep_first >= 0, "attn_window_decode: %d kept first positions", keep_first);
     TI_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attn_window_decode: the distance term needs both of its constants");
     if (check_pages("attn_window_decode", k_pages, v_pages, page_table, table_width, page_size, n_pages)) return 1;
     Pages pg{k_pages, v_pages, page_table, table_width, page_size, n_pages};
@@ -724,11 +836,12 @@ extern "C" int ti_attn_window_decode(const void* q, long long q_stride, void* ou
             }
             TI_CUDA(ti_launch_class<3>(attn_window_decode_kernel<T, OT, GH, VPL, MODE>, dim3(splits, n_heads * maps / GH, n_seq),
                                        dim3(DEC_WARPS * 32), smem, stream, (const T*)q, q_stride, (OT*)out, o_stride, seq_len, seq_slot, pg,
-                                       r1, r2, pb, n_heads, n_kv_heads, maps, dim, vdim, scale, window, splits, part_o, part_ml));
+                                       r1, r2, pb, n_heads, n_kv_heads, maps, dim, vdim, scale, window, window > 0 ? keep_first : 0, out_scale, splits,
+                                       part_o, part_ml));
             TI_CHECK_LAUNCH("attn_window_decode");
             if (splits > 1) {
                 TI_CUDA(ti_launch_class<4>(attn_window_merge_kernel<OT, MODE>, dim3(n_heads * maps, n_seq), dim3(64), 0, stream,
-                                           (const float*)part_o, (const float*)part_ml, (OT*)out, o_stride, n_heads * maps, vdim, splits));
+                                           (const float*)part_o, (const float*)part_ml, (OT*)out, o_stride, n_heads * maps, vdim, splits, out_scale));
                 TI_CHECK_LAUNCH("attn_window_merge");
             }
             return 0;
@@ -755,7 +868,7 @@ extern "C" int ti_attn_window_decode(const void* q, long long q_stride, void* ou
 // The merge alone, for partial results that another kernel left (the tensor-core kernel for single tokens): part_o
 // [n_seq, virtual heads, splits, vdim], part_ml [n_seq, virtual heads, splits, 2] -> out [n_seq, virtual heads * vdim].
 extern "C" int ti_attn_window_merge(const float* part_o, const float* part_ml, void* out, long long o_stride, int out_f32, int n_seq,
-                                    int n_virtual, int vdim, int splits, int mode, int dtype, cudaStream_t stream) {
+                                    int n_virtual, int vdim, int splits, int mode, float out_scale, int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_virtual > 0 && vdim > 0 && splits >= 1 && part_o && part_ml, "attn_window_merge: bad sizes");
     TI_REQUIRE(mode == 0 || mode == 1, "attn_window_merge: unknown mode %d", mode);
@@ -764,7 +877,7 @@ extern "C" int ti_attn_window_merge(const float* part_o, const float* part_ml, v
         auto go = [&](auto ot, auto md) -> int {
             using OT = decltype(ot);
             TI_CUDA(ti_launch_class<4>(attn_window_merge_kernel<OT, decltype(md)::value>, dim3(n_virtual, n_seq), dim3(64), 0, stream, part_o,
-                                       part_ml, (OT*)out, o_stride, n_virtual, vdim, splits));
+                                       part_ml, (OT*)out, o_stride, n_virtual, vdim, splits, out_scale));
             TI_CHECK_LAUNCH("attn_window_merge");
             return 0;
         };

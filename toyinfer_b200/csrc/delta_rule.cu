@@ -19,7 +19,8 @@
 // shared memory, the next run's on their way meanwhile; the state's columns come and go through shared
 // memory.
 //
-// head_gated_rmsnorm: y = o / rms(o) * w * sigmoid(gate) per token and head over vdim, w [vdim]
+// head_gated_rmsnorm: y = o / rms(o) * w * act(gate) * out_scale per token and head over vdim, w [vdim] or none (ones);
+//   act is the sigmoid or silu
 // shared by the heads.
 #include "common.cuh"
 
@@ -247,8 +248,8 @@ delta_rule_scan_kernel(const float* __restrict__ qn, const float* __restrict__ k
 // one warp per (token, head)
 template <typename T>
 __global__ void head_gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride,
-                                          const float* __restrict__ w, T* __restrict__ out, long long rows, int n_heads, int vdim,
-                                          float eps) {
+                                          const float* __restrict__ w, T* __restrict__ out, long long out_stride, long long rows,
+                                          int n_heads, int vdim, float eps, int gate_silu, float out_scale) {
     ti_pdl_trigger();
     ti_pdl_sync();
     o = ti_dependent(o); gate = ti_dependent(gate);
@@ -261,10 +262,11 @@ __global__ void head_gated_rmsnorm_kernel(const float* __restrict__ o, const T* 
     float ss = 0.f;
     for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
     ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)vdim + eps);
+    const float inv = rsqrtf(ss / (float)vdim + eps) * out_scale;
     for (int i = lane; i < vdim; i += 32) {
         const float gl = to_f32(gate[(size_t)m * gate_stride + (size_t)h * vdim + i]);
-        out[(size_t)r * vdim + i] = from_f32<T>(orow[i] * inv * w[i] / (1.0f + expf(-gl)));
+        const float ga = (gate_silu ? gl : 1.0f) / (1.0f + expf(-gl));
+        out[(size_t)m * out_stride + (size_t)h * vdim + i] = from_f32<T>(orow[i] * inv * (w ? w[i] : 1.0f) * ga);
     }
 }
 
@@ -313,17 +315,18 @@ extern "C" int ti_delta_rule_scan(const void* q, const void* k, const void* v, l
     });
 }
 
-// o: float32 [M, heads * vdim]; gate: [M, heads * vdim] of the engine's type with row stride gate_stride; w: float32 [vdim];
-// out: [M, heads * vdim] dense.
-extern "C" int ti_head_gated_rmsnorm(const float* o, const void* gate, long long gate_stride, const float* w, void* out, int M,
-                                     int n_heads, int vdim, float eps, int dtype, cudaStream_t stream) {
+// o: float32 [M, heads * vdim]; gate: [M, heads * vdim] of the engine's type with row stride gate_stride; w: float32 [vdim]
+// or null (ones); out: [M, heads * vdim] with row stride out_stride; gate_silu: the gate is silu(logit), else sigmoid(logit).
+extern "C" int ti_head_gated_rmsnorm(const float* o, const void* gate, long long gate_stride, const float* w, void* out,
+                                     long long out_stride, int M, int n_heads, int vdim, float eps, int gate_silu, float out_scale,
+                                     int dtype, cudaStream_t stream) {
     if (M == 0) return 0;
     TI_REQUIRE(M > 0 && n_heads > 0 && vdim > 0, "head_gated_rmsnorm: bad sizes");
     const long long rows = (long long)M * n_heads;
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         TI_CUDA(ti_launch_class<1>(head_gated_rmsnorm_kernel<T>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, stream, o, (const T*)gate,
-                                   gate_stride, w, (T*)out, rows, n_heads, vdim, eps));
+                                   gate_stride, w, (T*)out, out_stride, rows, n_heads, vdim, eps, gate_silu, out_scale));
         TI_CHECK_LAUNCH("head_gated_rmsnorm");
         return 0;
     });

@@ -336,3 +336,27 @@ extern "C" int ti_add_row_bias(const float* y, const float* bias, void* out, int
         return 0;
     });
 }
+
+// out[i] = a[i] * sa + b[i] * sb in 32-bit, rounded once
+template <typename T>
+__global__ void weighted_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b, float sb, T* __restrict__ out, long long total) {
+    ti_pdl_trigger();
+    ti_pdl_sync();
+    a = ti_dependent(a); b = ti_dependent(b);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<T>(fmaf(to_f32(a[i]), sa, to_f32(b[i]) * sb));
+}
+
+// a, b, out: dense, of the engine's type, `total` elements each.
+extern "C" int ti_weighted_sum(const void* a, float sa, const void* b, float sb, void* out, long long total, int dtype, cudaStream_t stream) {
+    if (total == 0) return 0;
+    TI_REQUIRE(total > 0, "weighted_sum: bad sizes");
+    const long long want = (total + 255) / 256;
+    return ti_dispatch_dtype(dtype, [&](auto t) -> int {
+        using T = decltype(t);
+        TI_CUDA(ti_launch_class<1>(weighted_sum_kernel<T>, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream, (const T*)a, sa,
+                                   (const T*)b, sb, (T*)out, total));
+        TI_CHECK_LAUNCH("weighted_sum");
+        return 0;
+    });
+}

@@ -3,8 +3,10 @@
 // Per head, with a state S [dim, vdim] in float32 that a sequence carries from token to token
 // (zero when the sequence starts):
 //     S_t = decay_h * S_{t-1} + k_t v_t^T,      o_t = S_t^T q_t
-// where q, k, v are the projections' outputs after silu (z / (1 + exp(-z)), applied here as
-// the values are loaded).  Everything of the recurrence is 32-bit.
+// where q, k, v are the projections' outputs after the entry function (`act` 1: silu,
+// z / (1 + exp(-z)); 0: as they are), applied here as the values are loaded, and k is then
+// multiplied by `k_scale` (a retention layer's dim^(-1/2); 1 otherwise).  Everything of the
+// recurrence is 32-bit.
 //
 // lightning_scan: a sequence's new tokens are scanned in order from the state in its slot,
 // which is updated in place: whole prompts, single tokens and anything between are one
@@ -28,6 +30,10 @@ namespace {
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
+// what q, k and v pass as they enter the recurrence
+struct Entry { int act; float k_scale; };
+__device__ __forceinline__ float enter(float z, int act) { return act ? silu_f(z) : z; }
+
 constexpr int SCAN_TOK = 16;     // tokens staged at a time
 
 template <typename T, int MAXD>
@@ -35,7 +41,7 @@ __global__ void lightning_scan_kernel(const T* __restrict__ q, const T* __restri
                                       long long q_stride, long long k_stride, long long v_stride,
                                       float* __restrict__ o, float* __restrict__ state, const float* __restrict__ decay,
                                       const int* __restrict__ cu_new, const int* __restrict__ seq_slot,
-                                      int n_heads, int dim, int vdim, int groups) {
+                                      int n_heads, int dim, int vdim, int groups, Entry en) {
     ti_pdl_trigger();
     extern __shared__ float sm[];        // q: [SCAN_TOK][dim], k: [SCAN_TOK][dim]
     ti_pdl_sync();
@@ -60,14 +66,14 @@ __global__ void lightning_scan_kernel(const T* __restrict__ q, const T* __restri
         for (int idx = threadIdx.x; idx < nt * dim; idx += blockDim.x) {
             const int tt = idx / dim, i = idx - tt * dim;
             const size_t tok = (size_t)(tok0 + t0 + tt);
-            qs[idx] = silu_f(to_f32(q[tok * q_stride + (size_t)h * dim + i]));
-            ks[idx] = silu_f(to_f32(k[tok * k_stride + (size_t)h * dim + i]));
+            qs[idx] = enter(to_f32(q[tok * q_stride + (size_t)h * dim + i]), en.act);
+            ks[idx] = enter(to_f32(k[tok * k_stride + (size_t)h * dim + i]), en.act) * en.k_scale;
         }
         __syncthreads();
         if (live) {
             for (int tt = 0; tt < nt; tt++) {
                 const size_t tok = (size_t)(tok0 + t0 + tt);
-                const float vv = silu_f(to_f32(v[tok * v_stride + (size_t)h * vdim + col]));
+                const float vv = enter(to_f32(v[tok * v_stride + (size_t)h * vdim + col]), en.act);
                 const float* kr = ks + tt * dim;
                 const float* qr = qs + tt * dim;
                 float acc = 0.f;
@@ -121,7 +127,7 @@ template <typename T>
 __global__ void __launch_bounds__(CT)
 lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, long long k_stride, long long v_stride,
                              float* __restrict__ U, const float* __restrict__ decay, Chunks cz, int n_heads, int dim,
-                             int vdim, int groups) {
+                             int vdim, int groups, Entry en) {
     ti_pdl_trigger();
     extern __shared__ float sm[];
     float* ks = sm;                      // [CH][128]  (lam^(nt-1-s) k_s, zero past dim)
@@ -148,8 +154,8 @@ lightning_chunk_local_kernel(const T* __restrict__ k, const T* __restrict__ v, l
 #pragma unroll
         for (int u = 0; u < 8; u++) {
             const int idx = (it + u) * CT + threadIdx.x, tt = idx >> 7, i = idx & 127;
-            ks[idx] = (tt < nt && i < dim) ? silu_f(x[u]) * pw[tt] : 0.f;
-            vs[idx] = (tt < nt && j0 + i < vdim) ? silu_f(y[u]) : 0.f;
+            ks[idx] = (tt < nt && i < dim) ? enter(x[u], en.act) * en.k_scale * pw[tt] : 0.f;
+            vs[idx] = (tt < nt && j0 + i < vdim) ? enter(y[u], en.act) : 0.f;
         }
     }
     __syncthreads();
@@ -231,7 +237,7 @@ __global__ void __launch_bounds__(CO)
 lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                            long long q_stride, long long k_stride, long long v_stride,
                            const float* __restrict__ U, float* __restrict__ o,
-                           const float* __restrict__ decay, Chunks cz, int n_heads, int dim, int vdim, int groups) {
+                           const float* __restrict__ decay, Chunks cz, int n_heads, int dim, int vdim, int groups, Entry en) {
     ti_pdl_trigger();
     extern __shared__ float sm[];
     ti_pdl_sync();
@@ -263,8 +269,8 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
         for (int u = 0; u < 8; u++) {
             const int idx = (it + u) * CO + tid, tt = idx >> 7, i = idx & 127;
             const bool ok = tt < nt && i < dim;
-            qs[tt * LDQ + i] = ok ? silu_f(x[u]) : 0.f;
-            kv[tt * LDQ + i] = ok ? silu_f(y[u]) : 0.f;
+            qs[tt * LDQ + i] = ok ? enter(x[u], en.act) : 0.f;
+            kv[tt * LDQ + i] = ok ? enter(y[u], en.act) * en.k_scale : 0.f;
         }
     }
     const float* Sg = U + ((size_t)blockIdx.y * n_heads + h) * dim * vdim;
@@ -312,7 +318,7 @@ lightning_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, con
 #pragma unroll
         for (int u = 0; u < 8; u++) {
             const int idx = (it + u) * CO + tid, tt = idx >> 7, j = idx & 127;
-            kv[idx] = (tt < nt && j0 + j < vdim) ? silu_f(x[u]) : 0.f;
+            kv[idx] = (tt < nt && j0 + j < vdim) ? enter(x[u], en.act) : 0.f;
         }
     }
     float acc[4][4];
@@ -393,11 +399,12 @@ int column_threads(int vdim) { return vdim <= 32 ? 32 : vdim <= 64 ? 64 : 128; }
 
 }  // namespace
 
-// q, k: [M, heads, dim], v: [M, heads, vdim] (token strides given), before silu.  o: float32 [M, heads * vdim].
-// state: float32 [slots, heads, dim, vdim].
+// q, k: [M, heads, dim], v: [M, heads, vdim] (token strides given), before the entry function (act 1: silu, 0: none;
+// k then times k_scale).  o: float32 [M, heads * vdim].  state: float32 [slots, heads, dim, vdim].
 extern "C" int ti_lightning_scan(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
                                  long long v_stride, float* o, float* state, const float* decay, const int* cu_new,
-                                 const int* seq_slot, int n_seq, int n_heads, int dim, int vdim, int dtype, cudaStream_t stream) {
+                                 const int* seq_slot, int n_seq, int n_heads, int dim, int vdim, int act, float k_scale,
+                                 int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_heads > 0 && dim > 0 && vdim > 0, "lightning_scan: bad sizes");
     const int threads = column_threads(vdim), groups = (vdim + threads - 1) / threads;
@@ -408,7 +415,7 @@ extern "C" int ti_lightning_scan(const void* q, const void* k, const void* v, lo
             constexpr int MAXD = decltype(md)::value;
             TI_CUDA(ti_launch(lightning_scan_kernel<T, MAXD>, dim3(n_heads * groups, n_seq), dim3(threads), smem, stream,
                               (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, o, state, decay, cu_new,
-                              seq_slot, n_heads, dim, vdim, groups));
+                              seq_slot, n_heads, dim, vdim, groups, Entry{act, k_scale}));
             TI_CHECK_LAUNCH("lightning_scan");
             return 0;
         });
@@ -420,13 +427,14 @@ extern "C" int ti_lightning_scan(const void* q, const void* k, const void* v, lo
 extern "C" int ti_lightning_chunked(const void* q, const void* k, const void* v, long long q_stride, long long k_stride,
                                     long long v_stride, float* o, float* state, float* U, const float* decay,
                                     const int* cu_new, const int* seq_slot, int n_seq, int n_chunks, int n_heads, int dim,
-                                    int vdim, int dtype, cudaStream_t stream) {
+                                    int vdim, int act, float k_scale, int dtype, cudaStream_t stream) {
     if (n_seq == 0 || n_chunks == 0) return 0;
     TI_REQUIRE(n_seq > 0 && n_seq <= 65535 && n_chunks > 0 && n_chunks <= 65535 && n_heads > 0 && n_heads <= 65535 && dim > 0 && vdim > 0,
                "lightning_chunked: bad sizes");
     TI_REQUIRE(dim <= 128, "lightning: heads of %d query/key elements are not supported (up to 128)", dim);
     const int groups = (vdim + VG - 1) / VG;
     Chunks cz{cu_new, seq_slot, n_seq};
+    const Entry en{act, k_scale};
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         const size_t smem1 = (size_t)(CH * 128 + CH * VG) * sizeof(float);
@@ -438,14 +446,14 @@ extern "C" int ti_lightning_chunked(const void* q, const void* k, const void* v,
             configured = true;
         }
         TI_CUDA(ti_launch(lightning_chunk_local_kernel<T>, dim3(n_heads * groups, n_chunks), dim3(CT), smem1, stream,
-                          (const T*)k, (const T*)v, k_stride, v_stride, U, decay, cz, n_heads, dim, vdim, groups));
+                          (const T*)k, (const T*)v, k_stride, v_stride, U, decay, cz, n_heads, dim, vdim, groups, en));
         TI_CHECK_LAUNCH("lightning_chunk_local");
         TI_CUDA(ti_launch(lightning_chunk_scan_kernel, dim3((dim * vdim + 127) / 128, n_heads, n_seq), dim3(128), 0, stream,
                           U, state, decay, cz, n_heads, dim, vdim));
         TI_CHECK_LAUNCH("lightning_chunk_scan");
         TI_CUDA(ti_launch(lightning_chunk_out_kernel<T>, dim3(n_heads * groups, n_chunks), dim3(CO), smem3, stream,
                           (const T*)q, (const T*)k, (const T*)v, q_stride, k_stride, v_stride, (const float*)U, o, decay, cz,
-                          n_heads, dim, vdim, groups));
+                          n_heads, dim, vdim, groups, en));
         TI_CHECK_LAUNCH("lightning_chunk_out");
         return 0;
     });

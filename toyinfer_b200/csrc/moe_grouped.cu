@@ -19,7 +19,7 @@
 // `moe_combine`: out[m] = sum_j z[m * top + j], summed in the order of j.
 //
 // The expert's activation (ACT_CLAMPED_SWISH): g' = min(g, limit), u' = clamp(u, -limit, limit),
-// y = g' * sigmoid(alpha * g') * (u' + 1).
+// y = g' * sigmoid(alpha * g') * (u' + shift).  (limit = infinity, alpha = 1, shift = 0: silu(g) * u.)
 // `relu2` (the dense feed-forward's activation, x -> max(x, 0)^2) is here as well.
 #include "common.cuh"
 
@@ -73,7 +73,7 @@ template <typename T, bool PAIR>
 __global__ void __launch_bounds__(G_THREADS)
 moe_grouped_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ W, const T* __restrict__ W2,
                    T* __restrict__ out, long long ldo, const int* __restrict__ perm, const int* __restrict__ off,
-                   int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha,
+                   int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha, float shift,
                    long long w_estride) {
     ti_pdl_trigger();
     __shared__ float As[GK][GM + 1];
@@ -159,7 +159,7 @@ moe_grouped_kernel(const T* __restrict__ a, long long lda, const T* __restrict__
                 // the two products are rounded to the engine's type first, as a kernel after the product would find them
                 const float g = fminf(to_f32(from_f32<T>(acc[i][j])), limit);
                 const float u = fminf(fmaxf(to_f32(from_f32<T>(acc2[i][j])), -limit), limit);
-                y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+                y = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
             } else {
                 y = acc[i][j] * scale;
             }
@@ -186,7 +186,7 @@ template <bool PAIR, int MI>
 __global__ void __launch_bounds__(T_THREADS)
 moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __restrict__ W, const bf16* __restrict__ W2,
                        bf16* __restrict__ out, long long ldo, const int* __restrict__ perm, const int* __restrict__ off,
-                       int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha,
+                       int n_experts, int N, int K, int top, int gather, int scatter, float scale, float limit, float alpha, float shift,
                        long long w_estride) {
     ti_pdl_trigger();
     constexpr int TM = 32 * MI;
@@ -305,7 +305,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, long long lda, const bf16* __
                 if constexpr (PAIR) {
                     const float gt = fminf(to_f32(from_f32<bf16>(acc[m][j][2 * half + c])), limit);
                     const float u = fminf(fmaxf(to_f32(from_f32<bf16>(acc2[m][j][2 * half + c])), -limit), limit);
-                    y = gt * (1.0f / (1.0f + expf(-alpha * gt))) * (u + 1.0f);
+                    y = gt * (1.0f / (1.0f + expf(-alpha * gt))) * (u + shift);
                 } else {
                     y = acc[m][j][2 * half + c] * scale;
                 }
@@ -376,7 +376,7 @@ __global__ void moe_gather_rows_kernel(const T* __restrict__ x, long long ldx, c
 }
 
 // the same over 16-byte pieces of bfloat16 (ff a multiple of 8)
-__global__ void moe_act_pair_vec_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y, int ff8, long long total, float limit, float alpha) {
+__global__ void moe_act_pair_vec_kernel(const bf16* __restrict__ gu, bf16* __restrict__ y, int ff8, long long total, float limit, float alpha, float shift) {
     ti_pdl_trigger();
     ti_pdl_sync();
     gu = ti_dependent(gu);
@@ -392,7 +392,7 @@ __global__ void moe_act_pair_vec_kernel(const bf16* __restrict__ gu, bf16* __res
         for (int e = 0; e < 8; e++) {
             const float g = fminf(to_f32(gp[e]), limit);
             const float u = fminf(fmaxf(to_f32(up[e]), -limit), limit);
-            op[e] = from_f32<bf16>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+            op[e] = from_f32<bf16>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift));
         }
         reinterpret_cast<uint4*>(y)[idx] = o4;
     }
@@ -417,9 +417,9 @@ __global__ void relu2_vec_kernel(const bf16* __restrict__ x, bf16* __restrict__ 
     }
 }
 
-// gu[i] = [gate (ff) | up (ff)] -> y[i] = g' sigmoid(alpha g') (u' + 1)
+// gu[i] = [gate (ff) | up (ff)] -> y[i] = g' sigmoid(alpha g') (u' + shift)
 template <typename T>
-__global__ void moe_act_pair_kernel(const T* __restrict__ gu, T* __restrict__ y, int ff, long long total, float limit, float alpha) {
+__global__ void moe_act_pair_kernel(const T* __restrict__ gu, T* __restrict__ y, int ff, long long total, float limit, float alpha, float shift) {
     ti_pdl_trigger();
     ti_pdl_sync();
     gu = ti_dependent(gu);
@@ -428,7 +428,7 @@ __global__ void moe_act_pair_kernel(const T* __restrict__ gu, T* __restrict__ y,
         const int f = (int)(idx - i * ff);
         const float g = fminf(to_f32(gu[i * 2 * ff + f]), limit);
         const float u = fminf(fmaxf(to_f32(gu[i * 2 * ff + ff + f]), -limit), limit);
-        y[idx] = from_f32<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+        y[idx] = from_f32<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift));
     }
 }
 
@@ -480,7 +480,7 @@ extern "C" int ti_moe_route_table(const int* ids, const int* table, int vocab, i
 // P places.  pair != 0: out[i, 0:N] = act(a_i W[e]^T, a_i W2[e]^T).  Else out[(scatter ? perm[i] : i)] = a_i W[e]^T * scale.
 extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const void* W2, void* out, long long ldo,
                               const int* perm, const int* off, int n_experts, int P, int N, int K, int top, int gather,
-                              int scatter, int pair, float scale, float limit, float alpha, long long w_estride, int dtype,
+                              int scatter, int pair, float scale, float limit, float alpha, float shift, long long w_estride, int dtype,
                               cudaStream_t stream) {
     if (P == 0) return 0;
     if (w_estride <= 0) w_estride = (long long)N * K;          // elements from one expert's matrix to the next
@@ -495,7 +495,7 @@ extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const
         const int nblk = (N + TN - 1) / TN;
         TI_REQUIRE(nblk <= 65535, "moe_grouped: %d weight rows are too many for one launch", N);
 #define TI_MOE_LAUNCH(PAIR, MI) TI_CUDA(ti_launch(moe_grouped_mma_kernel<PAIR, MI>, dim3(tiles, nblk), dim3(T_THREADS), 0, stream, (const bf16*)a, lda, \
-                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, w_estride))
+                              (const bf16*)W, (const bf16*)W2, (bf16*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, shift, w_estride))
         if (pair) { if (big) TI_MOE_LAUNCH(true, 2); else TI_MOE_LAUNCH(true, 1); }
         else { if (big) TI_MOE_LAUNCH(false, 2); else TI_MOE_LAUNCH(false, 1); }
 #undef TI_MOE_LAUNCH
@@ -509,10 +509,10 @@ extern "C" int ti_moe_grouped(const void* a, long long lda, const void* W, const
         using T = decltype(t);
         if (pair)
             TI_CUDA(ti_launch(moe_grouped_kernel<T, true>, dim3(tiles, nblk), dim3(G_THREADS), 0, stream, (const T*)a, lda,
-                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, w_estride));
+                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, shift, w_estride));
         else
             TI_CUDA(ti_launch(moe_grouped_kernel<T, false>, dim3(tiles, nblk), dim3(G_THREADS), 0, stream, (const T*)a, lda,
-                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, w_estride));
+                              (const T*)W, (const T*)W2, (T*)out, ldo, perm, off, n_experts, N, K, top, gather, scatter, scale, limit, alpha, shift, w_estride));
         TI_CHECK_LAUNCH("moe_grouped");
         return 0;
     });
@@ -555,14 +555,14 @@ extern "C" int ti_moe_gather_rows(const void* x, long long ldx, const int* pad_s
     });
 }
 
-extern "C" int ti_moe_act_pair(const void* gu, void* y, long long rows, int ff, float limit, float alpha, int dtype, cudaStream_t stream) {
+extern "C" int ti_moe_act_pair(const void* gu, void* y, long long rows, int ff, float limit, float alpha, float shift, int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
     TI_REQUIRE(rows > 0 && ff > 0, "moe_act_pair: bad sizes");
     if (dtype == TI_BF16 && ff % 8 == 0 && (((uintptr_t)gu | (uintptr_t)y) & 15) == 0) {
         const long long n = rows * (ff / 8);
         const long long want = (n + 255) / 256;
         TI_CUDA(ti_launch_class<1>(moe_act_pair_vec_kernel, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream,
-                                   (const bf16*)gu, (bf16*)y, ff / 8, n, limit, alpha));
+                                   (const bf16*)gu, (bf16*)y, ff / 8, n, limit, alpha, shift));
         TI_CHECK_LAUNCH("moe_act_pair");
         return 0;
     }
@@ -571,7 +571,7 @@ extern "C" int ti_moe_act_pair(const void* gu, void* y, long long rows, int ff, 
         const long long n = rows * ff;
         const long long want = (n + 255) / 256;
         TI_CUDA(ti_launch_class<1>(moe_act_pair_kernel<T>, dim3((unsigned)(want < 148 * 16 ? want : 148 * 16)), dim3(256), 0, stream,
-                                   (const T*)gu, (T*)y, ff, n, limit, alpha));
+                                   (const T*)gu, (T*)y, ff, n, limit, alpha, shift));
         TI_CHECK_LAUNCH("moe_act_pair");
         return 0;
     });

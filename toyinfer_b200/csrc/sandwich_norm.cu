@@ -96,7 +96,8 @@ __device__ __forceinline__ float gate_act(float g, int act) {
 }
 
 template <typename T>
-__global__ void gated_act_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int I, long long n, int pairs, int act) {
+__global__ void gated_act_kernel(const T* __restrict__ gu, long long ld, T* __restrict__ out, int I, long long n, int pairs, int act,
+                                 float limit) {
     ti_pdl_trigger();
     ti_pdl_sync();
     gu = ti_dependent(gu);
@@ -106,24 +107,31 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, long long ld, T* __re
         const T* row = gu + m * ld;
         const float g = to_f32(pairs ? row[2 * i] : row[i]);
         const float u = to_f32(pairs ? row[2 * i + 1] : row[I + i]);
-        out[idx] = from_f32<T>(gate_act(g, act) * u);
+        if (act == 2) {      // a clamped gate with a sharpened sigmoid, times the clamped up value plus one
+            const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+            out[idx] = from_f32<T>(gc / (1.0f + expf(-1.702f * gc)) * (uc + 1.0f));
+        } else {
+            out[idx] = from_f32<T>(gate_act(g, act) * u);
+        }
     }
 }
 
 }  // namespace
 
 // gu: [M, 2 I] with row stride ld: gate in the first I columns and up in the rest, or with `pairs` gate_i and up_i side
-// by side.  out: dense [M, I] = act(gate) * up, in 32-bit with one rounding.  act: 0 silu, 1 gelu (tanh form).
-extern "C" int ti_gated_act(const void* gu, long long ld, void* out, int M, int I, int pairs, int act, int dtype, cudaStream_t stream) {
+// by side.  out: dense [M, I] = act(gate) * up, in 32-bit with one rounding.  act: 0 silu, 1 gelu (tanh form); 2:
+// g' sigmoid(1.702 g') (u' + 1) with g' = min(gate, limit), u' = clamp(up, -limit, limit).
+extern "C" int ti_gated_act(const void* gu, long long ld, void* out, int M, int I, int pairs, int act, float limit, int dtype,
+                            cudaStream_t stream) {
     if (M == 0) return 0;
     TI_REQUIRE(M > 0 && I > 0 && ld >= 2LL * I, "gated_act: bad sizes M=%d I=%d", M, I);
-    TI_REQUIRE(act == 0 || act == 1, "gated_act: unknown activation %d", act);
+    TI_REQUIRE(act >= 0 && act <= 2, "gated_act: unknown activation %d", act);
     const long long n = (long long)M * I;
     const int threads = 256;
     const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
-        TI_CUDA(ti_launch_class<1>(gated_act_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, ld, (T*)out, I, n, pairs, act));
+        TI_CUDA(ti_launch_class<1>(gated_act_kernel<T>, dim3(blocks), dim3(threads), 0, stream, (const T*)gu, ld, (T*)out, I, n, pairs, act, limit));
         TI_CHECK_LAUNCH("gated_act");
         return 0;
     });

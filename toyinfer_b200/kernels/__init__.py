@@ -272,6 +272,19 @@ def linear_bias(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) 
     return out
 
 
+def weighted_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float) -> torch.Tensor:
+    """a * sa + b * sb, elementwise in 32-bit with one rounding; a and b dense, of one shape and type."""
+    _need_cuda(a, b, what="weighted_sum")
+    if a.shape != b.shape or a.dtype != b.dtype or not a.is_contiguous() or not b.is_contiguous():
+        raise KernelError("weighted_sum: expected two dense tensors of one shape and type")
+    from .lib import declare
+    out = torch.empty_like(a)
+    fn = declare("ti_weighted_sum", [ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong,
+                                     ctypes.c_int, ctypes.c_void_p])
+    _call(fn, _ptr(a), float(sa), _ptr(b), float(sb), _ptr(out), a.numel(), _code(a, "weighted_sum"), _stream())
+    return out
+
+
 def swiglu(gu: torch.Tensor, pairs: bool = False) -> torch.Tensor:
     """up * gate / (1 + exp(-gate)).  gu[M, 2*I] holds gate in its first I columns and up in
     the rest, or with ``pairs`` gate_i and up_i side by side."""
@@ -284,11 +297,11 @@ def swiglu(gu: torch.Tensor, pairs: bool = False) -> torch.Tensor:
     return out
 
 
-def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, act: str = "silu") -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, act: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """x[M, K] times w_pairs[2*I, K] (rows gate_0, up_0, gate_1, up_1, ...) followed by the
-    gated activation act(gate) * up -> [M, I]; act "silu" or "gelu_tanh".  The activation runs in the
-    product's epilogue where the tensor-core kernel takes the shape, else as a kernel of its own.
-    x may be a PendingNorm."""
+    gated activation act(gate) * up -> [M, I]; act "silu" or "gelu_tanh", or "clamped_swish" with its ``limit``
+    (see ``gated_act``).  The activation runs in the product's epilogue where the tensor-core kernel takes the
+    shape and knows the activation, else as a kernel of its own.  x may be a PendingNorm."""
     if act not in GATE_ACTS:
         raise KernelError(f"linear_swiglu: unknown activation {act!r}; known: {sorted(GATE_ACTS)}")
     if isinstance(x, PendingNorm):
@@ -305,11 +318,11 @@ def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, act: str = "silu") -> 
     M, K = x.shape
     N = w_pairs.shape[0]
     ldx, ldw = _row_stride(x, "linear x"), _row_stride(w_pairs, "linear w")
-    if gemm.tc_eligible(x, w_pairs, K, ldx, ldw):
+    if gemm.tc_eligible(x, w_pairs, K, ldx, ldw) and act in ("silu", "gelu_tanh"):
         out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
         gemm.run(x, w_pairs, out, M, N, K, ldx, ldw, gated=1 + GATE_ACTS[act])      # the kernels' codes: 1 silu, 2 gelu
         return out
-    return swiglu(linear(x, w_pairs), pairs=True) if act == "silu" else gated_act(linear(x, w_pairs), act, pairs=True)
+    return swiglu(linear(x, w_pairs), pairs=True) if act == "silu" else gated_act(linear(x, w_pairs), act, pairs=True, limit=limit)
 
 
 def qk_norm_rope_store(q, k, v, q_w, k_w, eps, tables, batch, mem) -> None:
@@ -530,13 +543,14 @@ def testing_wait_runs_out(limit: int = 10000) -> bool:
     return bool(flag.item())
 
 
-GATE_ACTS = {"silu": 0, "gelu_tanh": 1}
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
 
-def gated_act(gu: torch.Tensor, act: str, pairs: bool = False) -> torch.Tensor:
+def gated_act(gu: torch.Tensor, act: str, pairs: bool = False, limit: float = 0.0) -> torch.Tensor:
     """act(gate) * up in 32-bit with one rounding.  gu[M, 2*I] (rows may be strided) holds gate in its first I columns
-    and up in the rest, or with ``pairs`` gate_i and up_i side by side.  act: "silu" or "gelu_tanh"
-    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    and up in the rest, or with ``pairs`` gate_i and up_i side by side.  act: "silu", "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), or "clamped_swish": g' sigmoid(1.702 g') (u' + 1) with
+    g' = min(gate, limit) and u' = clamp(up, -limit, limit)."""
     _need_cuda(gu, what="gated_act")
     if act not in GATE_ACTS:
         raise KernelError(f"gated_act: unknown activation {act!r}; known: {sorted(GATE_ACTS)}")
@@ -546,6 +560,7 @@ def gated_act(gu: torch.Tensor, act: str, pairs: bool = False) -> torch.Tensor:
     from .lib import declare
     out = torch.empty((M, two_i // 2), dtype=gu.dtype, device=gu.device)
     fn = declare("ti_gated_act", [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                  ctypes.c_int, ctypes.c_int, ctypes.c_void_p])
-    _call(fn, _ptr(gu), gu.stride(0), _ptr(out), M, two_i // 2, 1 if pairs else 0, GATE_ACTS[act], _code(gu, "gated_act"), _stream())
+                                  ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_void_p])
+    _call(fn, _ptr(gu), gu.stride(0), _ptr(out), M, two_i // 2, 1 if pairs else 0, GATE_ACTS[act], float(limit), _code(gu, "gated_act"),
+          _stream())
     return out

@@ -14,9 +14,14 @@ CHUNK = 64                 # tokens per chunk of the chunked form (csrc/lightnin
 CHUNKED_FROM = 32          # new tokens of one sequence from which a step runs the chunked form (three launches)
 
 
-def mix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, batch) -> torch.Tensor:
-    """q, k [M, heads, dim] and v [M, heads, vdim] before their silu; ``state`` float32 [slots, heads, dim, vdim] is read
-    at each sequence's slot and left as it is after the step's tokens.  Returns float32 [M, heads * vdim]."""
+def mix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, batch,
+        act: str = "silu", k_scale: float = 1.0) -> torch.Tensor:
+    """q, k [M, heads, dim] and v [M, heads, vdim] as projected: they pass ``act`` ("silu" or "none") as they enter the
+    recurrence, and k is then multiplied by ``k_scale``; ``state`` float32 [slots, heads, dim, vdim] is read at each
+    sequence's slot and left as it is after the step's tokens.  Returns float32 [M, heads * vdim]."""
+    if act not in ("silu", "none"):
+        raise KernelError(f"lightning: unknown entry function {act!r}")
+    a = 1 if act == "silu" else 0
     _need_cuda(q, k, v, state, decay, what="lightning")
     M, nh, dim = q.shape
     vdim = v.shape[2]
@@ -34,13 +39,13 @@ def mix(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, 
     if batch.max_new >= CHUNKED_FROM:
         n_chunks = (batch.n_tok + CHUNK - 1) // CHUNK + batch.n_seq
         U = torch.empty((n_chunks, nh, dim, vdim), dtype=torch.float32, device=q.device)
-        _call(_fn("ti_lightning_chunked", [P, P, P, L, L, L, P, P, P, P, P, P, I, I, I, I, I, I, P]),
+        _call(_fn("ti_lightning_chunked", [P, P, P, L, L, L, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P]),
               _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(o), _ptr(state), _ptr(U), _ptr(decay),
-              _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, n_chunks, nh, dim, vdim, code, _stream(), launches=3)
+              _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, n_chunks, nh, dim, vdim, a, float(k_scale), code, _stream(), launches=3)
     else:
-        _call(_fn("ti_lightning_scan", [P, P, P, L, L, L, P, P, P, P, P, I, I, I, I, I, P]),
+        _call(_fn("ti_lightning_scan", [P, P, P, L, L, L, P, P, P, P, P, I, I, I, I, I, F, I, P]),
               _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(o), _ptr(state), _ptr(decay),
-              _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, nh, dim, vdim, code, _stream())
+              _ptr(batch.cu_new), _ptr(batch.seq_slot), batch.n_seq, nh, dim, vdim, a, float(k_scale), code, _stream())
     return o
 
 

@@ -41,13 +41,16 @@ def route_by_table(ids: torch.Tensor, table: torch.Tensor, n_experts: int):
 TC_MIN_GROUP = 64          # places per expert on average from which the tcgen05 grouped product runs (groups are padded to 128)
 
 
-def experts_ffn(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
-                limit: float, alpha: float, weight: float) -> torch.Tensor:
-    """x[M, H]; w_gate_up [experts, 2 * ff, H] (an expert's gate rows, then its up rows); w_down [experts, H, ff].  Every
-    pair's expert output times ``weight``, summed per token in the order of its choices -> [M, H].
+def expert_pairs(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                 limit: float, alpha: float, shift: float = 1.0, weight: float = 1.0):
+    """Every (token, choice) pair's expert output, not yet summed: x[M, H]; w_gate_up [experts, 2 * ff, H] (an expert's gate
+    rows, then its up rows); w_down [experts, H, ff]; the expert's activation is g' sigmoid(alpha g') (u' + shift) with
+    g' = min(g, limit), u' = clamp(u, -limit, limit) (limit = inf, alpha = 1, shift = 0: silu(g) u).  Returns
+    (z, place_of_pair): pair p's row, times ``weight``, is z[place_of_pair[p]], or z[p] when place_of_pair is None.
 
     bfloat16 steps with many tokens per expert pad every expert's tokens to tiles of 128 rows and run both products on
-    tcgen05 (csrc/gemm_tcgen05_grouped.cu); everything else runs the grouped tiles of csrc/moe_grouped.cu."""
+    tcgen05 (csrc/gemm_tcgen05_grouped.cu; ``weight`` is then left to the caller's sum); everything else runs the grouped
+    tiles of csrc/moe_grouped.cu."""
     _need_cuda(x, perm, off, w_gate_up, w_down, what="moe")
     M, H = x.shape
     E, ff2, H2 = w_gate_up.shape
@@ -73,27 +76,73 @@ def experts_ffn(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate_u
         grouped = _fn("ti_linear_grouped_tc", [P, P, P, P, I, I, I, I, L, P])
         gu = torch.empty((rows, 2 * ff), dtype=x.dtype, device=dev)
         _call(grouped, _ptr(xs), _ptr(w_gate_up), _ptr(gu), _ptr(tile_group), rows, E, 2 * ff, H, 2 * ff, _stream())
-        y = torch.empty((rows, ff), dtype=x.dtype, device=dev)
-        _call(_fn("ti_moe_act_pair", [P, P, L, I, F, F, I, P]), _ptr(gu), _ptr(y), rows, ff, float(limit), float(alpha), code, _stream())
+        y = act_pair(gu, limit, alpha, shift)
         z = torch.empty((rows, H), dtype=x.dtype, device=dev)
         _call(grouped, _ptr(y), _ptr(w_down), _ptr(z), _ptr(tile_group), rows, E, H, ff, H, _stream())
-        out = torch.empty((M, H), dtype=x.dtype, device=dev)
-        _call(_fn("ti_moe_combine_indexed", [P, P, P, I, I, I, F, I, P]), _ptr(z), _ptr(pad_of_pair), _ptr(out), M, H, top, float(weight),
-              code, _stream())
-        return out
-    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, L, I, P])
+        return z, pad_of_pair, True
+    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, F, L, I, P])
     y = torch.empty((Pn, ff), dtype=x.dtype, device=x.device)
     w_up = w_gate_up[:, ff:]          # the same storage, an expert's up rows after its gate rows
     _call(fn, _ptr(x), x.stride(0), _ptr(w_gate_up), _ptr(w_up), _ptr(y), ff, _ptr(perm), _ptr(off), E, Pn, ff, H, top, 1, 0, 1,
-          1.0, float(limit), float(alpha), 2 * ff * H, code, _stream())
+          1.0, float(limit), float(alpha), float(shift), 2 * ff * H, code, _stream())
     z = torch.empty((Pn, H), dtype=x.dtype, device=x.device)
     _call(fn, _ptr(y), ff, _ptr(w_down), None, _ptr(z), H, _ptr(perm), _ptr(off), E, Pn, H, ff, top, 0, 1, 0,
-          float(weight), 0.0, 0.0, 0, code, _stream())
+          float(weight), 0.0, 0.0, 0.0, 0, code, _stream())
+    return z, None, False
+
+
+def act_pair(gu: torch.Tensor, limit: float, alpha: float, shift: float = 1.0) -> torch.Tensor:
+    """gu [rows, 2 * ff] dense, a row's gate values and then its up values -> g' sigmoid(alpha g') (u' + shift) with
+    g' = min(g, limit), u' = clamp(u, -limit, limit), [rows, ff], in 32-bit with one rounding."""
+    _need_cuda(gu, what="moe_act_pair")
+    if gu.dim() != 2 or gu.shape[1] % 2 or not gu.is_contiguous():
+        raise KernelError("moe_act_pair: expected a dense [rows, 2 * ff] tensor")
+    rows, ff = gu.shape[0], gu.shape[1] // 2
+    y = torch.empty((rows, ff), dtype=gu.dtype, device=gu.device)
+    _call(_fn("ti_moe_act_pair", [P, P, L, I, F, F, F, I, P]), _ptr(gu), _ptr(y), rows, ff, float(limit), float(alpha), float(shift),
+          _code(gu, "moe"), _stream())
+    return y
+
+
+def experts_ffn(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                limit: float, alpha: float, weight: float) -> torch.Tensor:
+    """``expert_pairs`` with shift 1, every pair's output times ``weight``, summed per token in the order of its choices
+    -> [M, H]."""
+    M, H = x.shape
+    z, place, padded = expert_pairs(x, perm, off, w_gate_up, w_down, top, limit, alpha, 1.0, weight)
+    code = _code(x, "moe")
+    if padded:
+        out = torch.empty((M, H), dtype=x.dtype, device=x.device)
+        _call(_fn("ti_moe_combine_indexed", [P, P, P, I, I, I, F, I, P]), _ptr(z), _ptr(place), _ptr(out), M, H, top, float(weight),
+              code, _stream())
+        return out
     if top == 1:
         return z
     out = torch.empty((M, H), dtype=x.dtype, device=x.device)
     _call(_fn("ti_moe_combine", [P, P, I, I, I, I, P]), _ptr(z), _ptr(out), M, H, top, code, _stream())
     return out
+
+
+def route_softmax(z: torch.Tensor, correction, n_experts: int, top: int, n_groups: int = 0, keep: int = 0, scale: float = 1.0):
+    """z float32 [M, >= experts] (rows may be strided) -> (perm int32 [M * top], off int32 [experts + 1], weight float32
+    [M * top]): with s = softmax(z) over the experts, every token's ``top`` experts by s + correction (float32 [experts] or
+    None), chosen only among the ``keep`` best of ``n_groups`` equal runs of neighbouring experts (a run's score: its
+    largest s + correction; ``n_groups`` <= 1: no runs); a pair's weight is its s over the sum of the token's chosen s, times
+    ``scale``.  The pairs come out grouped by expert (csrc/moe_router.cu)."""
+    _need_cuda(z, correction, what="moe_route_softmax")
+    if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1 or z.shape[1] < n_experts:
+        raise KernelError("moe_route_softmax: the router's logits must be float32 [tokens, experts] with dense rows")
+    if correction is not None and (correction.dtype != torch.float32 or tuple(correction.shape) != (n_experts,) or not correction.is_contiguous()):
+        raise KernelError("moe_route_softmax: the correction must be dense float32 [experts]")
+    M = z.shape[0]
+    dev = z.device
+    perm = torch.empty(M * top, dtype=torch.int32, device=dev)
+    off = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    scratch = torch.empty(M * top, dtype=torch.int32, device=dev)
+    weight = torch.empty(M * top, dtype=torch.float32, device=dev)
+    _call(_fn("ti_moe_route_softmax", [P, L, P, I, I, I, I, F, I, P, P, P, P, P]), _ptr(z), z.stride(0), _ptr(correction), int(n_experts),
+          int(top), int(n_groups), int(keep), float(scale), M, _ptr(perm), _ptr(off), _ptr(scratch), _ptr(weight), _stream())
+    return perm, off, weight
 
 
 def route_topk(z: torch.Tensor, n_experts: int, top: int):
@@ -147,14 +196,14 @@ def experts_relu2(x: torch.Tensor, perm: torch.Tensor, off: torch.Tensor, w_up: 
         z = torch.empty((rows, H), dtype=x.dtype, device=dev)
         _call(grouped, _ptr(y), _ptr(w_down), _ptr(z), _ptr(tile_group), rows, E, H, ff, H, _stream())
         return z, pad_of_pair
-    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, L, I, P])
+    fn = _fn("ti_moe_grouped", [P, L, P, P, P, L, P, P, I, I, I, I, I, I, I, I, F, F, F, F, L, I, P])
     u = torch.empty((Pn, ff), dtype=x.dtype, device=dev)
     _call(fn, _ptr(x), x.stride(0), _ptr(w_up), None, _ptr(u), ff, _ptr(perm), _ptr(off), E, Pn, ff, H, top, 1, 0, 0,
-          1.0, 0.0, 0.0, 0, code, _stream())
+          1.0, 0.0, 0.0, 0.0, 0, code, _stream())
     y = relu2(u)
     z = torch.empty((Pn, H), dtype=x.dtype, device=dev)
     _call(fn, _ptr(y), ff, _ptr(w_down), None, _ptr(z), H, _ptr(perm), _ptr(off), E, Pn, H, ff, top, 0, 1, 0,
-          1.0, 0.0, 0.0, 0, code, _stream())
+          1.0, 0.0, 0.0, 0.0, 0, code, _stream())
     return z, None
 
 

@@ -114,17 +114,26 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_logit: t
     return o
 
 
-def head_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, n_heads: int, eps: float) -> torch.Tensor:
+def head_gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: Optional[torch.Tensor], n_heads: int, eps: float,
+                       gate_act: str = "sigmoid", out: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
     """o float32 [M, heads * vdim], gate [M, heads * vdim] logits of the engine's type (rows may be strided), w float32
-    [vdim] -> o / rms(o) per head * w * sigmoid(gate), in the gate's type."""
-    _need_cuda(o, gate, w, what="head_gated_rmsnorm")
+    [vdim] or None (ones) -> o / rms(o) per head * w * act(gate) * out_scale, in the gate's type; ``gate_act`` is "sigmoid"
+    or "silu".  ``out`` [M, heads * vdim] (rows may be strided, e.g. columns of a wider buffer) takes the result."""
+    _need_cuda(o, gate, w, out, what="head_gated_rmsnorm")
     M, N = o.shape
     if o.dtype != torch.float32 or not o.is_contiguous() or tuple(gate.shape) != (M, N) or gate.stride(1) != 1 or N % n_heads:
         raise KernelError("head_gated_rmsnorm: o must be dense float32 and the gate of its shape")
-    _vec(w, N // n_heads, "head_gated_rmsnorm: the weight")
-    out = torch.empty((M, N), dtype=gate.dtype, device=o.device)
-    _call(_fn("ti_head_gated_rmsnorm", [P, P, L, P, P, I, I, I, F, I, P]), _ptr(o), _ptr(gate), gate.stride(0), _ptr(w), _ptr(out),
-          M, int(n_heads), N // n_heads, float(eps), _code(gate, "head_gated_rmsnorm"), _stream())
+    if gate_act not in ("sigmoid", "silu"):
+        raise KernelError(f"head_gated_rmsnorm: unknown gate function {gate_act!r}")
+    if w is not None:
+        _vec(w, N // n_heads, "head_gated_rmsnorm: the weight")
+    if out is None:
+        out = torch.empty((M, N), dtype=gate.dtype, device=o.device)
+    elif tuple(out.shape) != (M, N) or out.dtype != gate.dtype or out.stride(1) != 1:
+        raise KernelError("head_gated_rmsnorm: the result's place must be [tokens, heads * vdim] of the gate's type with dense rows")
+    _call(_fn("ti_head_gated_rmsnorm", [P, P, L, P, P, L, I, I, I, F, I, F, I, P]), _ptr(o), _ptr(gate), gate.stride(0), _ptr(w), _ptr(out),
+          out.stride(0), M, int(n_heads), N // n_heads, float(eps), 1 if gate_act == "silu" else 0, float(out_scale),
+          _code(gate, "head_gated_rmsnorm"), _stream())
     return out
 
 

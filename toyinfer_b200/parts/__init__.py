@@ -19,7 +19,7 @@ from .base import (
     unregister_part,
 )
 from . import (norms, rope, attention, latent_attention, lightning, mlp, block, parallel_block, ends,  # noqa: F401  (registration)
-               hyper_block, rglru, biased_attention, channel_delta, sandwich_block, window_attention, mamba2)
+               hyper_block, rglru, biased_attention, channel_delta, sandwich_block, window_attention, mamba2, side_by_side)
 from .model import DecoderModel, LayerSpec, ModelSpec, ScheduleEntry
 
 __all__ = [

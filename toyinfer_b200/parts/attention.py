@@ -71,6 +71,8 @@ class GQAAttention(Mixer):
         if position is not None:
             try:
                 self.pos = ctx.positions[position]
+                if getattr(self.pos, "pairing", "half") != "half":
+                    raise ValueError(f"attention at {prefix!r}: its kernels turn elements (e, e + rot / 2) together, the position encoding {position!r} pairs neighbours")
             except KeyError:
                 raise ValueError(f"attention at {prefix!r} names unknown position encoding {position!r}") from None
         self.w_qkv: Optional[torch.Tensor] = None

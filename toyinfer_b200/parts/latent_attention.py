@@ -46,6 +46,8 @@ class LatentAttention(Mixer):
         if self.rot:
             try:
                 self.pos = ctx.positions[position]
+                if getattr(self.pos, "pairing", "half") != "half":
+                    raise ValueError(f"attention at {prefix!r}: its kernels turn elements (e, e + rot / 2) together, the position encoding {position!r} pairs neighbours")
             except KeyError:
                 raise ValueError(f"latent attention at {prefix!r} names unknown position encoding {position!r}") from None
             tables = getattr(self.pos, "dim", None)

@@ -56,19 +56,23 @@ register_part("feed_forward", "swiglu", SwiGLU)
 
 
 class GatedDense(FeedForward):
-    """y = Wdown (act(Wgate x) * (Wup x)) with ``act`` "gelu_tanh" or "silu"; no bias.  Gate and up rows are one matrix
-    with row 2i the gate's and row 2i + 1 the up's i-th, so one product makes both and the activation runs in that
-    product's epilogue on the tensor-core kernels (kernels.linear_swiglu), in 32-bit with one rounding."""
+    """y = Wdown (act(Wgate x) * (Wup x)) with ``act`` "gelu_tanh" or "silu"; or, with ``act`` "clamped_swish" and its
+    ``limit``, y = Wdown (g sigmoid(1.702 g) (u + 1)) with g = min(Wgate x, limit) and u = clamp(Wup x, -limit, limit);
+    no bias.  Gate and up rows are one matrix with row 2i the gate's and row 2i + 1 the up's i-th, so one product makes
+    both and the activation runs in that product's epilogue on the tensor-core kernels (kernels.linear_swiglu), in
+    32-bit with one rounding."""
 
     captures_start = True
 
-    def __init__(self, ctx: BuildContext, prefix: str, intermediate_size: int, act: str = "gelu_tanh",
+    def __init__(self, ctx: BuildContext, prefix: str, intermediate_size: int, act: str = "gelu_tanh", limit: float = 0.0,
                  names: Optional[Dict[str, str]] = None):
         self.hidden = ctx.hidden_size
         self.inter = int(intermediate_size)
         if act not in K.GATE_ACTS:
             raise ValueError(f"feed-forward at {prefix!r}: unknown activation {act!r}; known: {sorted(K.GATE_ACTS)}")
-        self.act = act
+        if act == "clamped_swish" and not float(limit) > 0:
+            raise ValueError(f"feed-forward at {prefix!r}: the clamped activation needs a positive limit, got {limit}")
+        self.act, self.limit = act, float(limit)
         n = {"gate": "gate", "up": "up", "down": "down"}
         n.update(names or {})
         self.names = {k: prefix + v for k, v in n.items()}
@@ -85,7 +89,7 @@ class GatedDense(FeedForward):
         self.w_down = tensors.pop(self.names["down"]).contiguous()
 
     def forward(self, x, batch) -> torch.Tensor:
-        return K.linear(K.linear_swiglu(x, self.w_gate_up, self.act), self.w_down)
+        return K.linear(K.linear_swiglu(x, self.w_gate_up, self.act, self.limit), self.w_down)
 
 
 class SquaredReLU(FeedForward):
@@ -237,3 +241,85 @@ class ScoredMoE(FeedForward):
 
 
 register_part("feed_forward", "scored_moe", ScoredMoE)
+
+
+class SoftmaxMoE(FeedForward):
+    """Mixture of silu-gated experts under a softmax router with a choice correction and expert groups: z = Wr x (float32),
+    s = softmax(z) over all experts; experts are CHOSEN by s + correction (a stored value per expert), only among the
+    experts of the ``keep`` best of ``n_groups`` equal runs of neighbouring experts (a run's score is its largest choice
+    score); the ``top`` chosen experts' outputs are weighted by their s, divided by the sum of the chosen s, times
+    ``scale``.  An expert: Wdown (silu(Wgate x) * (Wup x)); a shared expert of the same form (its own width) may run for
+    every token and is added as it is.  No biases.  The step's (token, choice) pairs are grouped by expert on the device
+    and every product runs once over all groups (kernels/moe.py)."""
+
+    captures_start = True
+
+    def __init__(self, ctx: BuildContext, prefix: str, n_experts: int, top: int, intermediate_size: int, n_groups: int = 0,
+                 keep: int = 0, scale: float = 1.0, correction: bool = True, shared_size: int = 0,
+                 names: Optional[Dict[str, str]] = None):
+        self.hidden = ctx.hidden_size
+        self.n_experts, self.top, self.inter, self.shared = int(n_experts), int(top), int(intermediate_size), int(shared_size)
+        self.n_groups, self.keep, self.scale, self.corrected = int(n_groups), int(keep), float(scale), bool(correction)
+        if not (1 <= self.top <= self.n_experts):
+            raise ValueError(f"moe at {prefix!r}: {self.top} of {self.n_experts} experts per token")
+        if self.n_groups > 1 and (self.n_experts % self.n_groups or not 1 <= self.keep <= self.n_groups
+                                  or self.keep * (self.n_experts // self.n_groups) < self.top):
+            raise ValueError(f"moe at {prefix!r}: {self.n_experts} experts in {self.n_groups} groups of which {self.keep} stay, "
+                             f"{self.top} per token")
+        n = {"expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "router": "router", "correction": "correction",
+             "shared": "shared."}
+        n.update(names or {})
+        self.prefix, self.n = prefix, n
+        self.w_gate_up = self.w_down = self.w_router = self.correction = self.ws_gate_up = self.ws_down = None
+
+    def _name(self, e: int, which: str) -> str:
+        return self.prefix + self.n["expert"].format(e) + self.n[which]
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        s: Dict[str, ParamSpec] = {}
+        for e in range(self.n_experts):
+            s[self._name(e, "gate")] = ParamSpec((self.inter, self.hidden), std=0.05)
+            s[self._name(e, "up")] = ParamSpec((self.inter, self.hidden), std=0.05)
+            s[self._name(e, "down")] = ParamSpec((self.hidden, self.inter), std=0.05)
+        s[self.prefix + self.n["router"]] = ParamSpec((self.n_experts, self.hidden), std=0.3)
+        if self.corrected:
+            s[self.prefix + self.n["correction"]] = ParamSpec((self.n_experts,), role="norm", init="normal", std=0.05)
+        if self.shared:
+            p = self.prefix + self.n["shared"]
+            s[p + self.n["gate"]] = ParamSpec((self.shared, self.hidden), std=0.05)
+            s[p + self.n["up"]] = ParamSpec((self.shared, self.hidden), std=0.05)
+            s[p + self.n["down"]] = ParamSpec((self.hidden, self.shared), std=0.05)
+        return s
+
+    def check_kernels(self, dtype) -> None:
+        if self.top > 16:
+            raise K.KernelError(f"moe: {self.top} experts per token are not supported (up to 16)")
+        if self.n_groups > 64:
+            raise K.KernelError(f"moe: {self.n_groups} expert groups are not supported (up to 64)")
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        E = range(self.n_experts)
+        # an expert's gate rows, then its up rows: one product makes both
+        self.w_gate_up = torch.stack([torch.cat([tensors.pop(self._name(e, "gate")), tensors.pop(self._name(e, "up"))], dim=0)
+                                      for e in E]).contiguous()
+        self.w_down = torch.stack([tensors.pop(self._name(e, "down")) for e in E]).contiguous()
+        self.w_router = tensors.pop(self.prefix + self.n["router"]).contiguous()
+        if self.corrected:
+            self.correction = tensors.pop(self.prefix + self.n["correction"]).to(torch.float32).contiguous()
+        if self.shared:
+            p = self.prefix + self.n["shared"]
+            g, u = tensors.pop(p + self.n["gate"]), tensors.pop(p + self.n["up"])
+            self.ws_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.shared, self.hidden).contiguous()
+            self.ws_down = tensors.pop(p + self.n["down"]).contiguous()
+
+    def forward(self, x, batch) -> torch.Tensor:
+        from ..kernels import moe as KM
+        M = x.shape[0]
+        z = K.linear(x, self.w_router, out_dtype=torch.float32)
+        perm, off, weight = KM.route_softmax(z, self.correction, self.n_experts, self.top, self.n_groups, self.keep, self.scale)
+        y, place, _ = KM.expert_pairs(x, perm, off, self.w_gate_up, self.w_down, self.top, float("inf"), 1.0, 0.0)
+        shared = K.linear(K.linear_swiglu(x, self.ws_gate_up, "silu"), self.ws_down) if self.shared else None
+        return KM.combine_gated(y, place, weight, shared, None, M, self.top)
+
+
+register_part("feed_forward", "softmax_moe", SoftmaxMoE)

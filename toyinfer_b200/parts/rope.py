@@ -1,4 +1,4 @@
-"""Rotary position encoding with half-rotation pairing.
+"""Rotary position encoding: the tables, and which elements of a head turn together.
 
 inv_freq_i = theta^(-2i/d) for i < d/2; the pair (x_i, x_{i+d/2}) of a head is
 rotated by the angle pos * inv_freq_i:
@@ -8,6 +8,9 @@ src/prefill.cu:185-208 (rotation).  The reference evaluates cosf/sinf of a 32-bi
 product in every kernel; here the angles are formed once, in 64-bit, into 32-bit
 cos and sin tables [max_positions, d/2] that every kernel reads, so that a
 position has one angle whichever way the tokens are cut into steps.
+
+``pairing`` "half" is the above; "neighbours" pairs (x_2i, x_2i+1) with the same angle pos * inv_freq_i
+(the tables are the same; a mixer whose kernel knows both reads the attribute).
 """
 from __future__ import annotations
 
@@ -77,7 +80,10 @@ class RotaryHalf(PositionEncoding):
     engine says how long its sequences get before the first step), not for the model's nominal limit."""
 
     def __init__(self, ctx: BuildContext, prefix: str, dim: int, theta: float, max_positions: int,
-                 scaling: Optional[dict] = None, lazy: bool = False):
+                 scaling: Optional[dict] = None, lazy: bool = False, pairing: str = "half"):
+        if pairing not in ("half", "neighbours"):
+            raise ValueError(f"rotary pairing must be 'half' or 'neighbours', got {pairing!r}")
+        self.pairing = pairing
         if dim % 2:
             raise ValueError(f"rotary dimension must be even, got {dim}")
         self.dim = int(dim)

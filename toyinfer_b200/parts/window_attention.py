@@ -1,5 +1,6 @@
-"""Two sliding-window attention mixers over keys and values of different sizes, on shared kernels
-(kernels/attention_window.py): attention with sigmoid weights, and differential attention.
+"""Three sliding-window attention mixers over keys and values of different sizes, on shared kernels
+(kernels/attention_window.py): attention with sigmoid weights, differential attention, and softmax attention under a
+window that keeps a sequence's first positions visible.
 
 Both: q = Wq x [heads, maps, dim], k = Wk x [kv_heads, maps, dim], v = Wv x [kv_heads, vdim]; query head h reads kv head
 h // (heads / kv_heads); key j is visible to the query at i when 0 <= i - j < window (window 0: every j <= i); y = Wo o.
@@ -18,6 +19,14 @@ of its own over the same values, a1 and a2; with lambda = exp(lq1 . lk1) - exp(l
     o = a1 - lambda a2;      o <- o / sqrt(mean(o^2) + eps) * (1 - diff);      o <- o * sigmoid(Wg x)_h
 
 per head.  The gate's rows ride with the q, k, v projection.
+
+``kept_window_attention`` (one map): biases on all four projections (each optional); every head of q and of k normed over
+its own elements with one weight [dim] for all heads; the first ``rot_dim`` elements of every head of q and k rotated by
+the token's position, in the pairing that the position encoding names; key j is visible to the query at i when
+0 <= i - j < window, or when j <= i and j < keep_first: the first ``keep_first`` positions of a sequence stay visible to
+every later query, at their own positions; softmax over the visible keys.  Its result may be scaled and placed in the
+columns of a wider buffer, and its projections' rows handed out, so that it can stand beside another mixer
+(parts/side_by_side.py).
 
 Keys and values of all positions live in the cache; a step first stores its own, then attends over the pages,
 whatever mix of new and cached tokens it brings.  Only the last ``window`` positions are ever read.
@@ -147,6 +156,8 @@ class DiffAttention(_WindowAttention):
             if position not in ctx.positions:
                 raise ValueError(f"attention at {prefix!r} names position encoding {position!r}, which the model does not have")
             self.position = ctx.positions[position]
+            if getattr(self.position, "pairing", "half") != "half":
+                raise ValueError(f"attention at {prefix!r}: its kernel turns elements (e, e + rot / 2) together, the position encoding {position!r} pairs neighbours")
         n = {"q": "q", "k": "k", "v": "v", "o": "o", "g": "g", "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
         n.update(names or {})
         self.names = {k: prefix + v for k, v in n.items()}
@@ -193,5 +204,97 @@ class DiffAttention(_WindowAttention):
             return K.linear(o, self.w_o)
 
 
+class KeptWindowAttention(_WindowAttention):
+    """Softmax attention under a sliding window that keeps the first ``keep_first`` positions visible (see the module's text)."""
+
+    def __init__(self, ctx: BuildContext, prefix: str, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 window: int, eps: float, keep_first: int = 0, position: Optional[str] = None, biases: bool = True,
+                 head_norm: bool = True, names: Optional[Dict[str, str]] = None):
+        self._sizes(ctx, prefix, n_heads, n_kv_heads, dim, vdim, scale, window, eps)
+        if int(keep_first) < 0:
+            raise ValueError(f"attention at {prefix!r}: {keep_first} kept first positions")
+        self.keep_first = int(keep_first) if self.window > 0 else 0
+        self.biases, self.head_norm = bool(biases), bool(head_norm)
+        self.position = None
+        if position is not None:
+            if position not in ctx.positions:
+                raise ValueError(f"attention at {prefix!r} names position encoding {position!r}, which the model does not have")
+            self.position = ctx.positions[position]
+        n = {"q": "q", "k": "k", "v": "v", "o": "o", "q_norm": "q.norm", "k_norm": "k.norm", "bias": ".b"}
+        n.update(names or {})
+        self.n = n
+        self.w_qkv = self.w_o = self.b_qkv = self.b_o = self.q_w = self.k_w = None
+
+    def _name(self, k: str, bias: bool = False) -> str:
+        return self.prefix + self.n[k] + (self.n["bias"] if bias else "")
+
+    @property
+    def n_in(self) -> int:
+        return self.n_heads * self.dim + self.n_kv * (self.dim + self.vdim)
+
+    @property
+    def n_out(self) -> int:
+        return self.n_heads * self.vdim
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, G, d, vd = self.n_heads, self.n_kv, self.dim, self.vdim
+        small = lambda shape, **kw: ParamSpec(shape, role="norm", **kw)
+        s = {self._name("q"): ParamSpec((H * d, self.hidden), std=0.05), self._name("k"): ParamSpec((G * d, self.hidden), std=0.05),
+             self._name("v"): ParamSpec((G * vd, self.hidden), std=0.05), self._name("o"): ParamSpec((self.hidden, H * vd), std=0.05)}
+        if self.biases:
+            for k, rows in (("q", H * d), ("k", G * d), ("v", G * vd), ("o", self.hidden)):
+                s[self._name(k, True)] = small((rows,), init="normal", std=0.1)
+        if self.head_norm:
+            s[self._name("q_norm")] = small((d,), init="one_plus_normal", std=0.1)
+            s[self._name("k_norm")] = small((d,), init="one_plus_normal", std=0.1)
+        return s
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        t = lambda name: tensors.pop(name)
+        f32 = lambda name: t(name).to(torch.float32).contiguous()
+        self.w_qkv = torch.cat([t(self._name(k)) for k in ("q", "k", "v")], dim=0).contiguous()
+        self.w_o = t(self._name("o")).contiguous()
+        if self.biases:
+            self.b_qkv = torch.cat([f32(self._name(k, True)) for k in ("q", "k", "v")]).contiguous()
+            self.b_o = f32(self._name("o", True))
+        if self.head_norm:
+            self.q_w, self.k_w = f32(self._name("q_norm")), f32(self._name("k_norm"))
+
+    def launch_plan(self, n_seq: int, plan_len: int, dtype, device, n_live=None):
+        span = min(plan_len, self.window + self.keep_first) if self.window > 0 else plan_len
+        return ("kept_window", KW.decode_splits(n_seq, self.n_heads, KW.heads_per_block(self.n_heads, self.n_kv), span, sm_count(device)))
+
+    # -- what a mixer that stands beside another hands out (parts/side_by_side.py) --
+    def in_rows(self):
+        """(the rows of the projection that ``mix`` reads, float32 biases of those rows or None)."""
+        return self.w_qkv, self.b_qkv
+
+    def out_cols(self):
+        """(the output projection [hidden, n_out], its float32 bias or None)."""
+        return self.w_o, self.b_o
+
+    def mix(self, qkv: torch.Tensor, batch, mem, out: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> torch.Tensor:
+        """qkv [M, n_in] as projected, without biases (rows may be strided; changed in place) -> the heads' outputs times
+        ``out_scale``, [M, n_out], in ``out`` when given."""
+        self._memory(mem)
+        H, G, d, vd = self.n_heads, self.n_kv, self.dim, self.vdim
+        M = qkv.shape[0]
+        tables = self.position.rotary_tables() if self.position is not None else None
+        pairing = getattr(self.position, "pairing", "half")
+        KW.head_prepare(qkv, self.b_qkv, self.q_w, self.k_w, self.eps, tables, pairing, H, G, d, vd, mem, batch)
+        return KW.attend(qkv[:, :H * d].view(M, H, d), 1, vd, mem,
+                         self.scale, self.window, "softmax", batch, k=qkv[:, H * d:(H + G) * d],
+                         v=qkv[:, (H + G) * d:(H + G) * d + G * vd], keep_first=self.keep_first, out_scale=out_scale, out=out)
+
+    def forward(self, x, batch, mem, shared) -> torch.Tensor:
+        with ranged(batch, "mixer.qkv"):
+            qkv = K.linear(x, self.w_qkv)
+        with ranged(batch, "mixer.attention"):
+            a = self.mix(qkv, batch, mem)
+        with ranged(batch, "mixer.out"):
+            return K.linear_bias(a, self.w_o, self.b_o)
+
+
 register_part("mixer", "sigmoid_attention", SigmoidAttention)
+register_part("mixer", "kept_window_attention", KeptWindowAttention)
 register_part("mixer", "diff_attention", DiffAttention)
