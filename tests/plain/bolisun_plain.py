@@ -192,15 +192,23 @@ def layer_tensors(weights: Dict[str, torch.Tensor], layer: int, part: str) -> Di
     return {k[len(pre):]: v.to(F64) for k, v in weights.items() if k.startswith(pre)}
 
 
+def read_streams(X: torch.Tensor, c: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """What a sublayer reads of the streams X [T, S, width]; without connection tensors there is one stream, read as it is."""
+    return torch.einsum("s,nsw->nw", c["in"], X) if c else X[:, 0]
+
+
 def connect(X: torch.Tensor, y: torch.Tensor, c: Dict[str, torch.Tensor]) -> torch.Tensor:
-    """X [T, S, width] -> the streams after a sublayer's output y [T, width] has been written."""
+    """X [T, S, width] -> the streams after a sublayer's output y [T, width] has been written (a plain sum without
+    connection tensors)."""
+    if not c:
+        return X + y[:, None, :]
     return torch.einsum("st,nsw->ntw", c["mix"], X) + c["out"][None, :, None] * y[:, None, :]
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int]) -> Tuple[torch.Tensor, List[torch.Tensor]]:
     """Returns (logits [T, vocab], the sum of the streams after every layer run)."""
     eps = float(cfg["norm"]["eps"])
-    S = int(cfg.get("streams", 1))
+    S = int(cfg.get("streams") or 1)
     E = weights["embed"].to(F64)
     x = E[list(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
     X = x[:, None, :].repeat(1, S, 1)
@@ -211,13 +219,11 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int]) 
             src = cfg["layers"][src]["weights_of"]
         w = lambda name: weights[f"l{src}.{name}"].to(F64)
         c1 = layer_tensors(weights, src, "hc1")
-        u = torch.einsum("s,nsw->nw", c1["in"], X)
-        y = parallel_mixer(rms_norm(u, w("norm1"), eps), layer_tensors(weights, src, "mix"), L["mixer"], eps)
+        y = parallel_mixer(rms_norm(read_streams(X, c1), w("norm1"), eps), layer_tensors(weights, src, "mix"), L["mixer"], eps)
         X = connect(X, y, c1)
         if L.get("mlp") is not None:
             c2 = layer_tensors(weights, src, "hc2")
-            u = torch.einsum("s,nsw->nw", c2["in"], X)
-            y = feed_forward(rms_norm(u, w("norm2"), eps), layer_tensors(weights, src, "mlp"), L["mlp"])
+            y = feed_forward(rms_norm(read_streams(X, c2), w("norm2"), eps), layer_tensors(weights, src, "mlp"), L["mlp"])
             X = connect(X, y, c2)
         after.append(X.sum(dim=1))
     logits = rms_norm(X.sum(dim=1), weights["final.norm"], eps) @ E.T
