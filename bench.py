@@ -18,7 +18,7 @@ error of the logits of a 512-token prompt's last place and of 8 decoded places.
 Every decode step reads all weights (8 GB) and the live sequences' cache, far more than
 the 126 MB L2, so nothing is flushed between steps.
 
-``--design kadodra`` (or ``tusasun``, ``bagasun``) measures another design instead (see run_design): prompt and decode rates and
+``--design kadodra`` (or ``tusasun``, ``bagasun``, ``bolisun``) measures another design instead (see run_design): prompt and decode rates and
 the device time of every stage of a layer at real layer sizes, beside the dense model at equal size.
 """
 from __future__ import annotations
@@ -509,6 +509,28 @@ def _bagasun_config(width, heads, layers, kind, vocab=32000):
             "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
 
 
+def _bolisun_config(width, heads, layers, kind, vocab=32000):
+    """``layers`` equal layers over four residual streams whose mixer is softmax attention under a window of 1,024 positions
+    that keeps the first four (heads of 128, 4 query heads per kv head, half of every head rotated with stretched
+    frequencies) beside retention (half as many heads, keys and values of 128), before a feed-forward of one kind: "dense"
+    (a clamped gate, 8/3 width) or "experts" (sixteen silu-gated experts of half the model's width in four groups of which
+    two stay, two per token, and a shared one)."""
+    mixer = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                      "mask": {"size": 1024, "keep_first": 4},
+                      "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+             "right": {"heads": max(1, heads // 2), "dim": 128, "vdim": 128,
+                       "decay": [1.0 - 2.0 ** -(2 + 6 * h / max(1, heads // 2)) for h in range(max(1, heads // 2))]},
+             "left_scale": 0.8, "right_scale": 0.5}
+    if kind == "dense":
+        mlp = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128, "limit": 7.0}
+    else:
+        mlp = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+               "shared": {"ff": width // 2}}
+    layer = {"type": "parallel", "mixer": mixer, "mlp": mlp}
+    return {"architecture": "Bolisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "streams": 4,
+            "layers": [json.loads(json.dumps(layer)) for _ in range(layers)], "max_positions": 8192}
+
+
 def _qwen3_like(width, heads, layers, vocab=32000):
     """The dense model of the same width, head count and layers; its three feed-forward matrices of 8/3 width hold what the
     other design's two of 4 width (or its two active experts of three matrices each, 6 width... the nearest round size) hold."""
@@ -525,13 +547,20 @@ def run_design(name: str, widths, layers: int, tokens: int, batch: int, context:
     import torch
     from toyinfer_b200.engine import Engine
     from toyinfer_b200.tracing import Tracer
-    if name not in ("kadodra", "tusasun", "bagasun"):
-        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra, tusasun, bagasun)")
+    if name not in ("kadodra", "tusasun", "bagasun", "bolisun"):
+        raise SystemExit(f"bench.py: unknown design {name!r} (kadodra, tusasun, bagasun, bolisun)")
     for width in widths:
         heads = width // 128
         if name == "kadodra":
             models = [("kadodra latent+dense", _kadodra_config(width, heads, layers, "latent")),
                       ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
+                      ("qwen3 dense", _qwen3_like(width, heads, layers))]
+        elif name == "bolisun":     # streams, attention and experts are Tusasun's; the decayed state is lightning's; the window Bagasun's
+            models = [("bolisun window+retention, dense", _bolisun_config(width, heads, layers, "dense")),
+                      ("bolisun window+retention, experts", _bolisun_config(width, heads, layers, "experts")),
+                      ("tusasun attention+experts", _tusasun_config(width, heads, layers, "attention")),
+                      ("kadodra lightning+experts", _kadodra_config(width, heads, layers, "lightning")),
+                      ("bagasun sigmoid+dense", _bagasun_config(width, heads, layers, "sigmoid")),
                       ("qwen3 dense", _qwen3_like(width, heads, layers))]
         elif name == "bagasun":     # dense feed-forwards: the dense model is its closest relation; the decayed state is lightning's
             models = [("bagasun sigmoid+dense", _bagasun_config(width, heads, layers, "sigmoid")),
@@ -861,7 +890,7 @@ def main() -> int:
                     help="run one of the larger described workloads end to end instead (8B or 32B shape)")
     ap.add_argument("--prompt-steps", default="", help="time one prompt step of each of these lengths instead (comma-separated), "
                     "with --layers layers")
-    ap.add_argument("--design", default="", help="measure another design beside its closest relations at equal size instead: kadodra, tusasun or bagasun "
+    ap.add_argument("--design", default="", help="measure another design beside its closest relations at equal size instead: kadodra, tusasun, bagasun or bolisun "
                     "(with --widths, --layers, --tokens, --batch, --context)")
     ap.add_argument("--widths", default="2048,4096", help="with --design: model widths (heads of 128)")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="with --design: the prompt's tokens")

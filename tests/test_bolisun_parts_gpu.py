@@ -88,6 +88,9 @@ KEPT = [
     dict(n_heads=2, n_kv_heads=2, dim=12, vdim=36, window=9, keep_first=70),                # more kept than a window, past a page
     dict(n_heads=4, n_kv_heads=2, dim=64, vdim=128, window=200, keep_first=33, rot=dict(base=1e4, dims=64, scaling=dict(STRETCH, original=256))),
     dict(n_heads=4, n_kv_heads=1, dim=128, vdim=128, window=31, keep_first=2, rot=dict(base=1e4, dims=32)),
+    # sizes that the tensor-core kernels take in bfloat16: kept positions that end inside a second tile; a window of a tile
+    dict(n_heads=4, n_kv_heads=2, dim=128, vdim=128, window=70, keep_first=66),
+    dict(n_heads=2, n_kv_heads=2, dim=64, vdim=64, window=64, keep_first=1, rot=dict(base=1e4, dims=64)),
 ]
 
 
@@ -110,6 +113,35 @@ def make_kept(dtype, c, hidden=56, seed=3, **options):
     if rot:
         mcfg["rot"] = rot
     return m, short_names(w), mcfg
+
+
+def test_which_kernels_take_the_kept_window(monkeypatch):
+    """bfloat16 heads of 64 or 128 run prompts, pieces and single tokens on the tensor-core kernels, kept positions and
+    all; the CUDA-core kernels give the same within the rounding of the weights."""
+    from toyinfer_b200.kernels import attention_window as KW
+    dtype = torch.bfloat16
+    m, w, mcfg = make_kept(dtype, KEPT[-2])
+    xs = [loud_inputs(n, 56, 5 + n, [j for j in (0, 65, 66, 130) if j < n]).to(dtype) for n in (330, 67)]
+    calls = []
+    real = KW._fn
+
+    def spy(name, sig):
+        calls.append(name)
+        return real(name, sig)
+    monkeypatch.setattr(KW, "_fn", spy)
+    sch = schedules([330, 67])
+    got = {name: feed(m, m.memory_request(), xs, s_, dtype) for name, s_ in sch.items()}
+    assert "ti_attn_window_tc" in calls and "ti_attn_decode_mma_scored" in calls
+    assert "ti_attn_window" not in calls and "ti_attn_window_decode" not in calls
+    monkeypatch.setattr(KW, "tensor_cores", False)
+    calls.clear()
+    other = {name: feed(m, m.memory_request(), xs, s_, dtype) for name, s_ in sch.items()}
+    assert "ti_attn_window" in calls and "ti_attn_window_decode" in calls and "ti_attn_window_tc" not in calls
+    wants = [plain.window_attention(x.double(), w, mcfg, 1e-5) for x in xs]
+    for name in sch:
+        for g, o, want in zip(got[name], other[name], wants):
+            torch.testing.assert_close(g, want, **tol(dtype, 30.0), msg=lambda e: f"{name}, tensor cores: {e}")
+            torch.testing.assert_close(o, want, **tol(dtype, 30.0), msg=lambda e: f"{name}, CUDA cores: {e}")
 
 
 @pytest.mark.parametrize("dtype", DT)

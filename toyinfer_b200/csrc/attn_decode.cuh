@@ -25,6 +25,9 @@ struct DecodeArgs {
     // out_f32:  results as float32.
     const float* r1 = nullptr; const float* r2 = nullptr; const float* pb = nullptr; const float* table = nullptr;
     int maps = 1, sigmoid = 0, out_f32 = 0, far = 0;
+    // keep_first: a sequence's first so many positions stay visible behind the window (0: none); out_scale multiplies the
+    //           results (where the kernel writes them itself; a merge of splits takes the factor as its own argument).
+    int keep_first = 0; float out_scale = 1.f;
 };
 
 // One block per (sequence, head); threads over the head's elements.  A split that saw no

@@ -105,13 +105,18 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     const int slot = a.seq_slot[b];
     const int lo = a.window > 0 ? max(0, L - a.window) : 0;
     const int tile_lo = lo / TILE;
-    const int n_tiles = L > 0 ? (L - 1) / TILE - tile_lo + 1 : 0;
+    // The tiles in the order they are shared out among the splits: those of the kept first positions that lie before the
+    // window's first tile (tiles 0 .. keep_tiles - 1), then the window's own (from tile_lo on).
+    const int keep = (WIN && a.window > 0) ? a.keep_first : 0;
+    const int keep_tiles = min((keep + TILE - 1) / TILE, tile_lo);
+    const int n_tiles = L > 0 ? keep_tiles + (L - 1) / TILE - tile_lo + 1 : 0;
     const int per = (n_tiles + a.n_splits - 1) / a.n_splits;
-    const int my_lo = tile_lo + split * per;
-    const int my_n = dead ? 0 : max(0, min(my_lo + per, tile_lo + n_tiles) - my_lo);
+    const int my_lo = split * per;                     // in that order
+    const int my_n = dead ? 0 : max(0, min(my_lo + per, n_tiles) - my_lo);
+    auto tile_at = [&](int i) -> int { return my_lo + i < keep_tiles ? my_lo + i : tile_lo + my_lo + i - keep_tiles; };
 
-    auto issue = [&](int i) {      // tile my_lo + i into stage i % STAGES; one thread calls this
-        const int p0 = (my_lo + i) * TILE;
+    auto issue = [&](int i) {      // this split's tile i into stage i % STAGES; one thread calls this
+        const int p0 = tile_at(i) * TILE;
         const int row0 = a.ring_rows > 0 ? p0 % a.ring_rows : p0;
         const int pidx = row0 / TILE;
         int page = pidx < a.table_width ? a.page_table[(size_t)slot * a.table_width + pidx] : 0;
@@ -134,14 +139,15 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
     unsigned early = 0;
     if (t == 0)
         for (int i = 0; i < STAGES - 1 && i < my_n; i++)
-            if (FUSED || my_lo + i != newest_tile) { issue(i); early |= 1u << i; }
+            if (FUSED || tile_at(i) != newest_tile) { issue(i); early |= 1u << i; }
     ti_pdl_sync();
     if (t == 0)
         for (int i = 0; i < STAGES - 1 && i < my_n; i++)
             if (!((early >> i) & 1u)) issue(i);
 
     const bool store_new = FUSED && f.k != nullptr;
-    const bool has_newest = L > 0 && newest_tile >= my_lo && newest_tile < my_lo + my_n;
+    const int newest_at = keep_tiles + newest_tile - tile_lo;      // where the newest tile stands in the order
+    const bool has_newest = L > 0 && newest_at >= my_lo && newest_at < my_lo + my_n;
     if (FUSED) {
         const bf16* fq = ti_dependent(f.q);
         const bf16* fk = ti_dependent(f.k);
@@ -249,7 +255,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
                 for (int nt = 0; nt < 2; nt++)
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        const int pos = (my_lo + i) * TILE + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const int pos = tile_at(i) * TILE + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         tb[nt][e] = trow[e >> 1][min(max(L - 1 - pos, 0), a.far)];
                     }
             }
@@ -262,9 +268,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
         }
         const uint32_t kbase = smem_u32(smem + (size_t)stage * 2 * TILE_BYTES);
         const uint32_t vbase = kbase + TILE_BYTES;
-        const int p0 = (my_lo + i) * TILE;
+        const int p0 = tile_at(i) * TILE;
         const int key0 = warp * 16;                      // this warp's positions within the tile
-        const bool patched = store_new && my_lo + i == newest_tile;
+        const bool patched = store_new && tile_at(i) == newest_tile;
         const bool edge = p0 < lo || p0 + TILE > L || patched;      // some positions of the tile are out of range (or written by hand)
         if (patched) {
             // the newest position's key and value are not in the cache the tile was read from
@@ -282,7 +288,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             // lines outside [lo, L) may hold anything: clear this warp's such value rows
             for (int r = 0; r < 16; r++) {
                 const int p = p0 + key0 + r;
-                if (p < lo || p >= L)
+                if ((p < lo && p >= keep) || p >= L)
                     for (int d = lane * 8; d < HD; d += 256)
                         *reinterpret_cast<uint4*>(smem + (size_t)stage * 2 * TILE_BYTES + TILE_BYTES + tile_offset<HD>(key0 + r, d)) = make_uint4(0, 0, 0, 0);
             }
@@ -325,7 +331,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
                     // sigmoid(x) = 1 / (1 + 2^(-x log2(e)))
                     const float x2 = a.table ? fmaf(s[nt][e], -scale2, tb[nt][e])
                                              : -1.4426950408889634f * (fmaf(s[nt][e], a.scale, cb[r]) - c1[r] * log1pf(c2[r] * (float)(L - 1 - pos)));
-                    p[nt][e] = (pos >= lo && pos < L) ? __frcp_rn(1.f + ex2(x2)) : 0.f;
+                    p[nt][e] = ((pos >= lo || pos < keep) && pos < L) ? __frcp_rn(1.f + ex2(x2)) : 0.f;
                 }
             pf[0] = pack_bf16(p[0][0], p[0][1]);
             pf[1] = pack_bf16(p[0][2], p[0][3]);
@@ -339,7 +345,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 const int p = p0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const bool ok = !edge || (p >= lo && p < L);
+                const bool ok = !edge || ((p >= lo || p < keep) && p < L);
                 s[nt][e] = ok ? s[nt][e] * scale2 : -INFINITY;
                 mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
             }
@@ -450,7 +456,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_c
             fin_o[idx] = acc;
             if (d == 0) { fin_ml[r * 2] = m; fin_ml[r * 2 + 1] = l; }
         } else if (a.n_splits == 1) {
-            const float res = sig ? acc : (l > 0.f ? acc / l : 0.f);
+            const float res = (sig ? acc : (l > 0.f ? acc / l : 0.f)) * (WIN ? a.out_scale : 1.f);
             if (WIN && a.out_f32) ((float*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = res;
             else ((bf16*)a.out)[(size_t)b * a.o_stride + (size_t)h * HD + d] = __float2bfloat16_rn(res);
         } else {
@@ -671,12 +677,14 @@ int launch_win(const tiattn::DecodeArgs& a, int n_seq, cudaStream_t stream) {
 // is read instead when given), else a softmax per map.  q: [B, heads * maps, width / maps]; out: [B, heads * maps, width], bfloat16 or (out_f32)
 // float32, written here when n_splits == 1; else every split leaves part_o [B, heads * maps, splits, width] and part_ml
 // [B, heads * maps, splits, 2] (maximum and sum; both 0 under sigmoid) for the caller's merge.  bfloat16, pages of 64.
+// keep_first: a sequence's first so many positions stay visible behind the window; out_scale multiplies results that are
+// written here (one split).
 extern "C" int ti_attn_decode_mma_scored(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
                                          const int* page_table, int table_width, int page_size, int ring_rows, int n_pages,
                                          const int* seq_slot, const int* seq_len, int n_seq, int n_heads, int n_kv_heads,
                                          int maps, int width, float scale, int window, int sigmoid, const float* r1,
-                                         const float* r2, const float* pb, const float* table, int far, int n_splits, void* out,
-                                         long long o_stride,
+                                         const float* r2, const float* pb, const float* table, int far, int keep_first,
+                                         float out_scale, int n_splits, void* out, long long o_stride,
                                          int out_f32, float* part_o, float* part_ml, int dtype, cudaStream_t stream) {
     if (n_seq == 0) return 0;
     TI_REQUIRE(dtype == TI_BF16, "attention_decode (score rules): bfloat16 only");
@@ -699,6 +707,8 @@ extern "C" int ti_attn_decode_mma_scored(const void* q, long long q_stride, cons
     a.part_o = part_o; a.part_ml = part_ml;
     a.r1 = r1; a.r2 = r2; a.pb = pb; a.maps = maps; a.sigmoid = sigmoid; a.out_f32 = out_f32;
     a.table = sigmoid ? table : nullptr; a.far = far;
+    TI_REQUIRE(keep_first >= 0, "attention_decode (score rules): %d kept first positions", keep_first);
+    a.keep_first = window > 0 ? keep_first : 0; a.out_scale = out_scale;
     return width == 64 ? launch_win<64>(a, n_seq, stream) : launch_win<128>(a, n_seq, stream);
 }
 

@@ -63,6 +63,9 @@ struct Args {
     // (head, map); n_heads and n_kv_heads count real heads.  The output's row holds heads * maps results; with out_f32
     // they are stored as floats.
     int maps; int out_f32;
+    // The first keep_first positions of a sequence stay visible to every later query whatever the window (0: none);
+    // results are multiplied by out_scale before they are rounded.
+    int keep_first = 0; float out_scale = 1.f;
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -188,7 +191,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int lo_blk = (PAGED && a.window > 0) ? max(0, start + q0 - a.window + 1) : 0;
     const int pt_lo = lo_blk / BKV;
     const int n_old = (PAGED && active && lo_blk < start) ? (start - 1) / BKV - pt_lo + 1 : 0;
-    const int n_tiles = active ? n_old + last_q / BKV - kt_lo + 1 : 0;
+    // Kept first positions that the window's own tiles do not hold come first in a block's list of tiles: the pages of
+    // those below `start` (pages 0 .. n_kold - 1, all before page pt_lo), then the step's own tiles that hold the rest
+    // (tiles 0 .. n_kown - 1, all before tile kt_lo).
+    const int keep = (a.window > 0 && active) ? a.keep_first : 0;
+    const int n_kold = PAGED ? min((min(keep, start) + BKV - 1) / BKV, n_old > 0 ? pt_lo : (start + BKV - 1) / BKV) : 0;
+    const int n_kown = min((max(keep - start, 0) + BKV - 1) / BKV, kt_lo);
+    const int n_kept = n_kold + n_kown;
+    const int n_tiles = active ? n_kept + n_old + last_q / BKV - kt_lo + 1 : 0;
+    // tile j of the list: whether it is a page of old positions, and which page or which of the step's tiles
+    auto tile_of = [&](int j, bool& old) -> int {
+        if (j < n_kold) { old = true; return j; }
+        if (j < n_kept) { old = false; return j - n_kold; }
+        if (j < n_kept + n_old) { old = true; return pt_lo + j - n_kept; }
+        old = false;
+        return kt_lo + j - n_kept - n_old;
+    };
 
     if (active && warp_uniform() == 0) {
         if (elect_one()) {
@@ -199,8 +217,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // first product of tile j - 1 has read that buffer, the values of tile j once the second
             // product of tile j - 2 has read theirs.
             // the first row, in the tensor map of the pages, of the page that holds tile j of the old positions
-            auto page_row = [&](int j) -> int {
-                const int p0 = (pt_lo + j) * BKV;
+            auto page_row = [&](int pg) -> int {
+                const int p0 = pg * BKV;
                 const int pidx = (a.ring_rows > 0 ? p0 % a.ring_rows : p0) / BKV;
                 int page = pidx < a.table_width ? a.page_table[(size_t)slot * a.table_width + pidx] : 0;
                 if (page < 0 || page >= a.n_pages) page = 0;
@@ -211,15 +229,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (!mbar_wait(&k_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
                 unsigned char* ks = kv_s + (size_t)s * STAGE;
                 mbar_expect_tx(&k_full[s], K_BYTES);
-                if (PAGED && j < n_old) {
-                    const int y = page_row(j);
+                bool old;
+                const int t = tile_of(j, old);
+                if (PAGED && old) {
+                    const int y = page_row(t);
 #pragma unroll
                     for (int bx = 0; bx < HDK / 64; bx++) tma_load_2d(ks + bx * KBOX, &kp_map, map * HDK + bx * 64, y, &k_full[s]);
                     return true;
                 }
 #pragma unroll
                 for (int bx = 0; bx < HDK / 64; bx++)
-                    tma_load_2d(ks + bx * KBOX, &k_map, (kvh * a.maps + map) * HDK + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &k_full[s]);
+                    tma_load_2d(ks + bx * KBOX, &k_map, (kvh * a.maps + map) * HDK + bx * 64, tok0 + t * BKV, &k_full[s]);
                 return true;
             };
             auto load_v = [&](int j) -> bool {
@@ -227,14 +247,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (!mbar_wait(&v_empty[s], (uint32_t)(((j >> 1) & 1) ^ 1))) { ti_report(status, TI_STATUS_PIPE_WAIT); return false; }
                 unsigned char* vs = kv_s + (size_t)s * STAGE + K_BYTES;
                 mbar_expect_tx(&v_full[s], V_BYTES);
-                if (PAGED && j < n_old) {
-                    const int y = page_row(j);
+                bool old;
+                const int t = tile_of(j, old);
+                if (PAGED && old) {
+                    const int y = page_row(t);
 #pragma unroll
                     for (int bx = 0; bx < HDV / 64; bx++) tma_load_2d(vs + bx * KBOX, &vp_map, bx * 64, y, &v_full[s]);
                     return true;
                 }
 #pragma unroll
-                for (int bx = 0; bx < HDV / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HDV + bx * 64, tok0 + (kt_lo + j - n_old) * BKV, &v_full[s]);
+                for (int bx = 0; bx < HDV / 64; bx++) tma_load_2d(vs + bx * KBOX, &v_map, kvh * HDV + bx * 64, tok0 + t * BKV, &v_full[s]);
                 return true;
             };
             bool ok = n_tiles > 0 && load_k(0);
@@ -318,8 +340,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             if (ok && !mbar_wait(&s_full[sb], (uint32_t)((j >> 1) & 1))) { ti_report(status, TI_STATUS_MMA_WAIT); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
-            const bool old = PAGED && j < n_old;
-            const int tile0 = old ? (pt_lo + j) * BKV - start : (kt_lo + j - n_old) * BKV;   // the tile's first position
+            bool old;
+            const int tile_t = tile_of(j, old);
+            const int tile0 = old ? tile_t * BKV - start : tile_t * BKV;                    // the tile's first position
+            const int kept_below = keep - start;        // key positions below this one are among the kept first
             const int limit = old ? 0 : n;                                                  // where its valid keys end
             const int k0 = tile0 + half * HALF;
             // whether any of this warp's 32 rows masks any of these 32 keys: a key after the warp's first row, beyond
@@ -362,7 +386,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                         for (int u = 0; u < 2; u++) {
                             const int kj = k0 + e + u;
-                            const bool vis = ok && (!edge || (kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window)));
+                            const bool vis = ok && (!edge || (kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window || kj < kept_below)));
                             float y = v[e + u] * nscale2;
                             if (hb) y += __ldg(hb + min(max(qi - kj, 0), a.far));
                             w[u] = vis ? __fdividef(1.0f, 1.0f + ex2(fminf(y, 126.f))) : 0.f;
@@ -389,7 +413,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int e = 0; e < HALF; e++) {
                     const int kj = k0 + e;
-                    const bool vis = kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window);
+                    const bool vis = kj <= qi && kj < limit && (a.window <= 0 || kj > qi - a.window || kj < kept_below);
                     v[e] = vis ? v[e] : -INFINITY;
                 }
             }
@@ -440,7 +464,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 if (ok) {
                     const int st = (int)threadIdx.x - 64, row = st >> 2, part = st & 3;
                     const int p = tile0 + start + row;
-                    if (old ? (p < lo_blk || p >= start) : (tile0 + row >= n)) {
+                    if (old ? ((p < lo_blk && p >= keep) || p >= start) : (tile0 + row >= n)) {
                         constexpr int PART = HDV / 2;       // bytes of a row's HDV * 2 that one of its four threads clears
                         uint4* dst = reinterpret_cast<uint4*>(kv_s + (size_t)sb * STAGE + K_BYTES + (part * PART / 128) * KBOX +
                                                               row * 128 + (part * PART) % 128);
@@ -493,7 +517,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (a.sink != nullptr && m_used > -INFINITY) l_run += ex2(fminf(a.sink[h] * 1.4426950408889634f - m_used, 126.f));
         if (ok) {
             tc_fence_after();
-            const float inv = MODE == 1 ? 1.f : l_run > 0.f ? 1.f / l_run : 0.f;
+            const float inv = MODE == 1 ? a.out_scale : l_run > 0.f ? a.out_scale / l_run : 0.f;
             bf16* orow = (bf16*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)hv * HDV;
             float* orow32 = (float*)a.out + (size_t)(tok0 + qi) * a.o_stride + (size_t)hv * HDV;
 #pragma unroll 1
@@ -709,15 +733,18 @@ extern "C" int ti_attn_chunk_tc(const void* q, const void* k, const void* v, voi
 // of two); out [n_tokens, heads * maps * vdim], bfloat16 or (out_f32) float32 with
 // o_stride in elements of that type.  seq_start null: every sequence starts at position 0 and the pages are not read.
 // Otherwise k_pages [pages, kv_heads, 64, maps * dim] and v_pages [pages, kv_heads, 64, vdim] hold the positions
-// before the step's.  dist_bias: float32 [heads, far + 1] or null.  window <= 0: every earlier position.
+// before the step's.  dist_bias: float32 [heads, far + 1] or null.  window <= 0: every earlier position.  keep_first: a
+// sequence's first so many positions stay visible behind the window; out_scale multiplies the results.
 extern "C" int ti_attn_window_tc(const void* q, const void* k, const void* v, void* out,
                                  long long q_stride, long long k_stride, long long v_stride, long long o_stride, int out_f32,
                                  const int* cu_new, const int* seq_start, const int* seq_slot, int n_seq, int max_new,
                                  int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale, int window,
                                  int mode, const void* k_pages, const void* v_pages, const int* page_table, int table_width,
-                                 int page_size, int n_pages, const float* dist_bias, int far, cudaStream_t stream) {
+                                 int page_size, int n_pages, const float* dist_bias, int far, int keep_first, float out_scale,
+                                 cudaStream_t stream) {
     if (n_seq == 0 || max_new == 0) return 0;
     const char* what = "attention_window (tcgen05)";
+    TI_REQUIRE(keep_first >= 0, "%s: %d kept first positions", what, keep_first);
     TI_REQUIRE((dim == 64 || dim == 128) && (vdim == 64 || vdim == 128), "%s: heads of %d and %d elements (64 or 128 each)", what, dim, vdim);
     TI_REQUIRE(maps >= 1 && n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0, "%s: bad head counts", what);
     TI_REQUIRE(n_seq <= 65535 && n_tokens <= 65535 * BQ, "%s: too many sequences or tokens for one launch", what);
@@ -746,6 +773,7 @@ extern "C" int ti_attn_window_tc(const void* q, const void* k, const void* v, vo
     a.out = out; a.o_stride = o_stride; a.out_f32 = out_f32; a.maps = maps;
     a.seq_start = seq_start; a.seq_slot = seq_slot; a.page_table = page_table; a.table_width = table_width;
     a.ring_rows = 0; a.n_pages = n_pages; a.dist_bias = dist_bias; a.far = far;
+    a.keep_first = window > 0 ? keep_first : 0; a.out_scale = out_scale;
     auto go = [&](auto dk, auto dv) -> int {
         constexpr int DK = decltype(dk)::value, DV = decltype(dv)::value;
         if (mode == 1) return paged ? launch<DK, true, DV, 1>(qm, km, vm, kpm, vpm, a, n_seq, max_new, stream)

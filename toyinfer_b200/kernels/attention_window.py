@@ -153,14 +153,13 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
     o_dtype = torch.float32 if out_f32 else q.dtype
     if out is not None and (tuple(out.shape) != (M, HV * vdim) or out.dtype != o_dtype or out.stride(1) != 1 or not out.is_cuda):
         raise KernelError("attention_window: the result's place must be [tokens, heads * maps * vdim] of the result's type with dense rows")
-    plain = keep_first == 0 and out_scale == 1.0 and out is None      # the tensor-core kernels know no kept first positions
-    if batch.mode == "extend" and plain and tensor_cores and q.dtype == torch.bfloat16 and maps * dim == vdim and vdim in (64, 128) \
+    if batch.mode == "extend" and tensor_cores and q.dtype == torch.bfloat16 and maps * dim == vdim and vdim in (64, 128) \
             and dim % 8 == 0 and mem.page_size == 64 and (maps == 1 if mode == "sigmoid" else (r1 is None and pb is None)) \
             and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0:
         # single tokens on the tensor-core kernel that the dense model decodes with (csrc/attn_decode_mma.cu): a key row as
         # long as a value row, shared by the maps; weights are rounded to bfloat16 for the second product
         from .attention import decode_splits as tile_splits
-        span = min(batch.plan_len, window + mem.page_size) if window > 0 else batch.plan_len
+        span = min(batch.plan_len, window + keep_first + mem.page_size) if window > 0 else batch.plan_len
         splits = tile_splits(M, G, span, mem.page_size, sm_count(q.device), n_live=batch.n_real_seq)
         if out is None:
             out = torch.empty((M, HV * vdim), dtype=o_dtype, device=q.device)    # every row is a sequence's
@@ -171,10 +170,10 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
         use_table = mode == "sigmoid" and table is not None
         if use_table and (table.dtype != torch.float32 or table.dim() != 2 or table.shape[0] != H or not table.is_contiguous()):
             raise KernelError("attention_window: the distance table must be dense float32 [heads, far + 1]")
-        _call(_fn("ti_attn_decode_mma_scored", [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, I, F, I, I, P, P, P, P, I, I, P, L, I, P, P, I, P]),
+        _call(_fn("ti_attn_decode_mma_scored", [P, L, P, P, P, I, I, I, I, P, P, I, I, I, I, I, F, I, I, P, P, P, P, I, I, F, I, P, L, I, P, P, I, P]),
               _ptr(q), q.stride(0), pages[0], pages[1], pages[2], pages[3], pages[4], 0, pages[5], _ptr(batch.seq_slot),
               _ptr(batch.seq_len), M, H, G, maps, vdim, float(scale), int(window), MODES[mode], _ptr(r1), _ptr(r2), _ptr(pb),
-              _ptr(table) if use_table else None, table.shape[1] - 1 if use_table else 0, splits,
+              _ptr(table) if use_table else None, table.shape[1] - 1 if use_table else 0, keep_first, float(out_scale), splits,
               _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(part_o), _ptr(part_ml), code, _stream())
         if splits > 1:
             _call(_fn("ti_attn_window_merge", [P, P, P, L, I, I, I, I, I, I, F, I, P]), _ptr(part_o), _ptr(part_ml), _ptr(out), out.stride(0),
@@ -194,17 +193,18 @@ def attend(q: torch.Tensor, maps: int, vdim: int, mem, scale: float, window: int
               _ptr(r1), _ptr(r2), _ptr(pb), H, G, maps, dim, vdim, float(scale), int(window), keep_first, float(out_scale), MODES[mode], splits,
               _ptr(part_o), _ptr(part_ml), code, _stream(), launches=2 if splits > 1 else 1)
         return out
-    if plain and tensor_cores and q.dtype == torch.bfloat16 and dim in (64, 128) and vdim in (64, 128) and k is not None and v is not None \
+    if tensor_cores and q.dtype == torch.bfloat16 and dim in (64, 128) and vdim in (64, 128) and k is not None and v is not None \
             and mem.page_size == 64 and scale > 0 and (mode == "softmax" or table is not None) and (mode == "sigmoid" or r1 is None) \
-            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 and t.stride(-1) == 1 for t in (q, k, v)):
+            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 and t.stride(-1) == 1 for t in (q, k, v)) \
+            and out.stride(0) % (4 if out_f32 else 8) == 0 and out.data_ptr() % 16 == 0:
         if table is not None and (table.dtype != torch.float32 or table.dim() != 2 or table.shape[0] != H or not table.is_contiguous()):
             raise KernelError("attention_window: the distance table must be dense float32 [heads, far + 1]")
         start = batch.mode == "start"
-        _call(_fn("ti_attn_window_tc", [P, P, P, P, L, L, L, L, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, I, P, I, P]),
+        _call(_fn("ti_attn_window_tc", [P, P, P, P, L, L, L, L, I, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, I, P, I, I, F, P]),
               _ptr(q), _ptr(k), _ptr(v), _ptr(out), q.stride(0), k.stride(0), v.stride(0), out.stride(0), 1 if out_f32 else 0,
               _ptr(batch.cu_new), None if start else _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seq, batch.max_new, M, H, G,
               maps, dim, vdim, float(scale), int(window), MODES[mode], *pages, _ptr(table) if mode == "sigmoid" else None,
-              table.shape[1] - 1 if (mode == "sigmoid" and table is not None) else 0, _stream())
+              table.shape[1] - 1 if (mode == "sigmoid" and table is not None) else 0, keep_first, float(out_scale), _stream())
         return out
     _call(_fn("ti_attn_window", [P, L, P, L, I, P, P, P, I, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, F, I, I, F, I, I, P]),
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), 1 if out_f32 else 0, _ptr(batch.cu_new), _ptr(batch.seq_start),
