@@ -731,14 +731,14 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             batch = fill_batch(BatchBuffers(1, new, dev), "mixed", [0], [cached], [[0] * new], 1, cached + new)
             return (lambda: K.attention_chunk(q, k, v, mem, 1 / math.sqrt(hd), 0, batch)), \
                 qkv.numel() * 2 + new * nh * hd * 2 + 2 * cached * nkv * hd * 2, 4.0 * nh * hd * new * (cached + (new + 1) / 2)
-        if name.startswith("attn_window_prepare"):        # attn_window_prepare[:TOKENS[,sigmoid|diff]]: biases, norms, rotation, cache store
+        if name.startswith("attn_window_prepare"):        # attn_window_prepare[:TOKENS[,sigmoid|diff|kept]]: biases, norms, rotation, cache store
             from toyinfer_b200.kernels import attention_window as KW
             from toyinfer_b200.parts.rope import rotary_tables
             opts = name.split(":")[1].split(",") if ":" in name else []
             T = int(opts[0]) if opts else PREFILL_TOKENS
             kind = opts[1] if len(opts) > 1 else "sigmoid"
             nh, nkv = 16, 4
-            maps, hd, vd = (1, 128, 128) if kind == "sigmoid" else (2, 64, 128)
+            maps, hd, vd = (1, 128, 128) if kind in ("sigmoid", "kept") else (2, 64, 128)
             pages = (T + 63) // 64
             table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
             table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
@@ -752,17 +752,24 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             if kind != "sigmoid":
                 cos, sin = rotary_tables(hd, 1e6, T + 64)
                 tables = (cos.to(dev), sin.to(dev), hd)
+            if kind == "kept":          # Bolisun's form: biases, a norm per head, neighbouring pairs of half of each head rotated
+                cos, sin = rotary_tables(64, 1e6, T + 64)
+                tables = (cos.to(dev), sin.to(dev), 64)
+                bias, qw, kw_ = f32(nq + nk + nv), f32(hd), f32(hd)
+                return (lambda: KW.head_prepare(qkv, bias, qw, kw_, 1e-6, tables, "neighbours", nh, nkv, hd, vd, mem, batch)), \
+                    (2 * (nq + nk + nv) + nk + nv) * T * 2, 0.0
             # the projection's row read and written back, keys and values written to the pages
             return (lambda: KW.prepare(qkv, bias, qw, kw_, 1e-6, tables, nh, nkv, maps, hd, vd, mem, batch)), \
                 (2 * (nq + nk + nv) + nk + nv) * T * 2, 0.0
-        if name.startswith("attn_window_decode"):         # attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]]: one token per sequence
+        if name.startswith("attn_window_decode"):         # attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff|kept[,WINDOW]]]: one token per sequence
             from toyinfer_b200.kernels import attention_window as KW
             opts = name.split(":")[1].split(",") if ":" in name else []
             B, ctx = (int(opts[0]), int(opts[1])) if len(opts) > 1 else (8, 2048)
             kind = opts[2] if len(opts) > 2 else "sigmoid"
             window = int(opts[3]) if len(opts) > 3 else 1024
             nh, nkv = 16, 4
-            maps, hd, vd = (1, 128, 128) if kind == "sigmoid" else (2, 64, 128)
+            maps, hd, vd = (1, 128, 128) if kind in ("sigmoid", "kept") else (2, 64, 128)
+            keep = 4 if kind == "kept" else 0           # softmax under a window that keeps the first four positions
             per = (ctx + 63) // 64
             table = (torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per) + 1)
             table = torch.cat([table, torch.zeros(1, per, dtype=torch.int32, device=dev)]).contiguous()
@@ -772,12 +779,12 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             f32 = lambda *shape: torch.rand(*shape, generator=g, device=dev)
             r1, r2, pb = (f32(nh), f32(nh), -2 * f32(nh)) if kind == "sigmoid" else (None, None, None)
             tab = KW.distance_table(r1, r2, pb, nh, window, dev) if kind == "sigmoid" else None
-            seen = min(ctx, window)
+            seen = min(ctx, window + keep)
             # the visible keys and values are read once per kv head
             return (lambda: KW.attend(q, maps, vd, mem, hd ** -0.5, window, "sigmoid" if kind == "sigmoid" else "softmax", batch,
-                                      r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid", table=tab)), \
+                                      r1=r1, r2=r2, pb=pb, out_f32=kind == "diff", table=tab, keep_first=keep)), \
                 B * seen * nkv * (maps * hd + vd) * 2, 2.0 * B * seen * nh * maps * (hd + vd)
-        if name.startswith("attn_window"):                # attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]]: a whole prompt
+        if name.startswith("attn_window"):                # attn_window[:TOKENS[,sigmoid|diff|kept[,WINDOW[,cuda]]]]: a whole prompt
             from toyinfer_b200.kernels import attention_window as KW
             opts = name.split(":")[1].split(",") if ":" in name else []
             T = int(opts[0]) if opts else PREFILL_TOKENS
@@ -785,7 +792,8 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             window = int(opts[2]) if len(opts) > 2 else 1024
             KW.tensor_cores = not (len(opts) > 3 and opts[3] == "cuda")
             nh, nkv = 16, 4
-            maps, hd, vd = (1, 128, 128) if kind == "sigmoid" else (2, 64, 128)
+            maps, hd, vd = (1, 128, 128) if kind in ("sigmoid", "kept") else (2, 64, 128)
+            keep = 4 if kind == "kept" else 0           # softmax under a window that keeps the first four positions
             pages = (T + 63) // 64
             table = torch.zeros(2, pages, dtype=torch.int32, device=dev)
             table[0] = torch.arange(1, pages + 1, dtype=torch.int32, device=dev)
@@ -797,11 +805,11 @@ def run_kernel(name: str, reps: int, eager: bool = False):
             r1, r2, pb = (f32(nh), f32(nh), -2 * f32(nh)) if kind == "sigmoid" else (None, None, None)
             tab = KW.distance_table(r1, r2, pb, nh, window, dev) if kind == "sigmoid" else None
             KW.prepare(qkv, None, None, None, 1e-6, None, nh, nkv, maps, hd, vd, mem, batch)       # the keys and values into the pages
-            pairs = sum(min(i + 1, window) for i in range(T))
+            pairs = sum(min(i + 1, window) + min(max(i + 1 - window, 0), keep) for i in range(T))
             return (lambda: KW.attend(qkv[:, :nq].view(T, nh * maps, hd), maps, vd, mem, hd ** -0.5, window,
-                                      "sigmoid" if kind == "sigmoid" else "softmax", batch, r1=r1, r2=r2, pb=pb, out_f32=kind != "sigmoid",
-                                      k=qkv[:, nq:nq + nk], v=qkv[:, nq + nk:], table=tab)), \
-                qkv.numel() * 2 + T * nh * maps * vd * (2 if kind == "sigmoid" else 4), 2.0 * nh * maps * (hd + vd) * pairs
+                                      "sigmoid" if kind == "sigmoid" else "softmax", batch, r1=r1, r2=r2, pb=pb, out_f32=kind == "diff",
+                                      k=qkv[:, nq:nq + nk], v=qkv[:, nq + nk:], table=tab, keep_first=keep)), \
+                qkv.numel() * 2 + T * nh * maps * vd * (4 if kind == "diff" else 2), 2.0 * nh * maps * (hd + vd) * pairs
         if name.startswith("ssd_decode"):                 # ssd_decode[:BATCH]: one token per sequence through the Mamba-2 recurrence
             from toyinfer_b200.kernels import recurrent as KR
             B = int(name.split(":")[1]) if ":" in name else 8
@@ -883,7 +891,7 @@ def main() -> int:
     ap.add_argument("--kernel", default="", help="time one kernel alone instead: gemm_decode, gemm_decode_b64, gemm_down, "
                     "gemm_qkv, gemm_o, gemm_head, gemm_prefill, gemm:M,N,K[,BN,SPLITS], attn_decode[:BATCH,CONTEXT[,HEADS,KV_HEADS]], attn_decode_b64, attn_decode_b1, "
                     "attn_prefill[:TOKENS], attn_chunk[:CACHED,NEW[,HEAD_DIM]], add_rmsnorm[:TOKENS], rope_store[:TOKENS], "
-                    "attn_window[:TOKENS[,sigmoid|diff[,WINDOW[,cuda]]]], attn_window_prepare[:TOKENS[,sigmoid|diff]], attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff[,WINDOW]]], "
+                    "attn_window[:TOKENS[,sigmoid|diff|kept[,WINDOW[,cuda]]]], attn_window_prepare[:TOKENS[,sigmoid|diff|kept]], attn_window_decode[:BATCH,CONTEXT[,sigmoid|diff|kept[,WINDOW]]], "
                     "ssd_scan[:TOKENS[,SEGMENT]], ssd_decode[:BATCH], mma_issue; "
                     "ref:all or ref:<case> times the reference's kernel recompiled for sm_100a beside this library's")
     ap.add_argument("--workload", default="", choices=["", "8b", "32b"],

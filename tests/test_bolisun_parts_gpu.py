@@ -94,6 +94,67 @@ KEPT = [
 ]
 
 
+@pytest.mark.parametrize("dtype", DT)
+@pytest.mark.parametrize("pairing", ["half", "neighbours"])
+@pytest.mark.parametrize("H,G,dim,vdim,rot", [(3, 1, 48, 20, 12), (4, 2, 64, 128, 32), (2, 2, 128, 64, 128), (2, 1, 256, 256, 64), (5, 5, 128, 128, 0)])
+def test_heads_prepared_one_by_one(dtype, pairing, H, G, dim, vdim, rot):
+    """The kernel alone (a lane a run of elements for bfloat16 heads of 64, 128 and 256, a lane an element otherwise): biases,
+    one norm weight for all heads, either pairing of the rotation, rows of a wider projection, keys and values in their pages."""
+    from toyinfer_b200.cache import CacheManager
+    from toyinfer_b200.kernels import attention_window as KW
+    from toyinfer_b200.parts import KVRequest
+    from toyinfer_b200.parts.rope import rotary_tables
+    from test_kadodra_parts_gpu import batch_for
+    g = torch.Generator().manual_seed(dim + rot)
+    N = H * dim + G * (dim + vdim)
+    lens, starts = [70, 3], [5, 64]
+    M = sum(lens)
+    y = (torch.randn(M, N + 16, generator=g) * 2).to(dtype)
+    bias, qw, kw = torch.randn(N, generator=g), torch.rand(dim, generator=g) + 0.5, torch.rand(dim, generator=g) + 0.5
+    tables = None
+    if rot:
+        cos, sin = rotary_tables(rot, 1e3, 256)
+        tables = (cos.to(DEV), sin.to(DEV), rot)
+    cache = CacheManager([KVRequest(G, dim, 0, True, vdim if vdim != dim else 0)], 64 * 8, 2, 256, dtype, DEV)
+    slots = [cache.allocate_slot() for _ in lens]
+    for s_, st, n in zip(slots, starts, lens):
+        cache.reserve(s_, st + n)
+    cache.flush()
+    yd = y.to(DEV)
+    KW.head_prepare(yd[:, :N], bias.to(DEV), qw.to(DEV), kw.to(DEV), 1e-5, tables, pairing, H, G, dim, vdim, cache.view(0),
+                    batch_for("mixed", slots, starts, lens, cache.scratch_slot))
+    x = y[:, :N].double() + bias.double()
+    pos = torch.cat([torch.arange(st, st + n) for st, n in zip(starts, lens)])
+
+    def heads(t, n, w):
+        t = t.reshape(M, -1, n)
+        t = t / torch.sqrt((t * t).mean(-1, keepdim=True) + 1e-5) * w.double()
+        if rot:
+            c, s_ = cos.double()[pos][:, None, :], sin.double()[pos][:, None, :]
+            a, b = (t[..., 0:rot:2], t[..., 1:rot:2]) if pairing == "neighbours" else (t[..., :rot // 2], t[..., rot // 2:rot])
+            ra, rb = a * c - b * s_, b * c + a * s_
+            t = t.clone()
+            if pairing == "neighbours":
+                t[..., 0:rot:2], t[..., 1:rot:2] = ra, rb
+            else:
+                t[..., :rot // 2], t[..., rot // 2:rot] = ra, rb
+        return t.reshape(M, -1)
+    want = torch.cat([heads(x[:, :H * dim], dim, qw), heads(x[:, H * dim:(H + G) * dim], dim, kw), x[:, (H + G) * dim:]], dim=1)
+    torch.testing.assert_close(yd[:, :N].cpu().double(), want, **tol(dtype, 4.0))
+    assert torch.equal(yd[:, N:].cpu(), y[:, N:])                    # the columns after q, k, v are left alone
+    view = cache.view(0)
+    table = view.page_table.cpu()
+    o = 0
+    for s_, st, n in zip(slots, starts, lens):
+        for i in (0, n - 1):
+            p = st + i
+            page = int(table[s_, p // 64])
+            krow = view.k_pages[page, :, p % 64].reshape(-1).cpu()
+            vrow = view.v_pages[page, :, p % 64].reshape(-1).cpu()
+            assert torch.equal(krow, yd[o + i, H * dim:(H + G) * dim].cpu()) and torch.equal(vrow, yd[o + i, (H + G) * dim:N].cpu())
+        o += n
+
+
 def make_kept(dtype, c, hidden=56, seed=3, **options):
     from toyinfer_b200.parts import PartSpec, build_part
     c = dict(c)

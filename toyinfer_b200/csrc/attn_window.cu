@@ -452,6 +452,104 @@ __device__ __forceinline__ void load_run(const T* __restrict__ p, float (&x)[N],
     }
 }
 
+// The same for bfloat16 heads of 64, 128 or 256 elements on 16-byte-aligned rows: a lane holds E = n / 32 neighbouring
+// elements of the head in registers (one load of 4, 8 or 16 bytes, one store to the row and one to the cache), the sum of
+// squares is a warp's shuffle, a neighbour pair lies within a lane and a half pair in the lane rot / (2 E) further on.
+template <int E>
+__device__ __forceinline__ void head_prepare_lane(bf16* __restrict__ row, const float* __restrict__ bias, const float* __restrict__ w,
+                                                  float eps, const float* __restrict__ cs, const float* __restrict__ sn, int rot,
+                                                  int pairing, bf16* __restrict__ cache, int lane) {
+    constexpr int N = 32 * E;
+    const int i0 = lane * E;
+    float x[E];
+    load_run<bf16, E>(row + i0, x, true);
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; e++) {
+        if (bias) x[e] += bias[i0 + e];
+        ss = fmaf(x[e], x[e], ss);
+    }
+    if (w) {
+        const float inv = rsqrtf(warp_sum(ss) / (float)N + eps);
+#pragma unroll
+        for (int e = 0; e < E; e++) x[e] = x[e] * inv * w[i0 + e];
+    }
+    if (cs) {
+        const int half = rot >> 1;
+        if (pairing) {
+#pragma unroll
+            for (int e = 0; e < E; e += 2) {
+                if (i0 + e < rot) {
+                    const float c = cs[(i0 + e) >> 1], sv = sn[(i0 + e) >> 1], a = x[e], b = x[e + 1];
+                    x[e] = a * c - b * sv;
+                    x[e + 1] = b * c + a * sv;
+                }
+            }
+        } else {
+            const int hop = half / E;                   // lanes between the two elements of a pair (rot / 2 is a multiple of E)
+            const bool first = i0 < half;
+#pragma unroll
+            for (int e = 0; e < E; e++) {
+                const float o = __shfl_sync(0xffffffffu, x[e], first ? lane + hop : lane - hop);      // (lanes outside the rotation read anything)
+                if (i0 < rot) {
+                    const int f = first ? i0 + e : i0 + e - half;
+                    x[e] = first ? x[e] * cs[f] - o * sn[f] : x[e] * cs[f] + o * sn[f];
+                }
+            }
+        }
+    }
+    bf16 raw[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) raw[e] = from_f32<bf16>(x[e]);
+    if constexpr (E == 8) {
+        *reinterpret_cast<uint4*>(row + i0) = *reinterpret_cast<const uint4*>(raw);
+        if (cache) *reinterpret_cast<uint4*>(cache + i0) = *reinterpret_cast<const uint4*>(raw);
+    } else if constexpr (E == 4) {
+        *reinterpret_cast<uint2*>(row + i0) = *reinterpret_cast<const uint2*>(raw);
+        if (cache) *reinterpret_cast<uint2*>(cache + i0) = *reinterpret_cast<const uint2*>(raw);
+    } else {
+        *reinterpret_cast<uint32_t*>(row + i0) = *reinterpret_cast<const uint32_t*>(raw);
+        if (cache) *reinterpret_cast<uint32_t*>(cache + i0) = *reinterpret_cast<const uint32_t*>(raw);
+    }
+}
+
+__global__ void attn_head_prepare_vec_kernel(bf16* __restrict__ qkv, long long ld, const float* __restrict__ bias,
+                                             const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int pairing,
+                                             int max_pos, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                             const int* __restrict__ seq_slot, Pages pg, long long rows, int H, int G, int dim, int vdim) {
+    ti_pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int per = H + 2 * G;
+    const long long m = r / per;
+    const int j = (int)(r - m * per);
+    const int kind = j < H ? 0 : j < H + G ? 1 : 2;         // query, key, value
+    const int head = kind == 0 ? j : kind == 1 ? j - H : j - H - G;
+    const int n = kind == 2 ? vdim : dim;
+    const int off = kind == 0 ? head * dim : kind == 1 ? H * dim + head * dim : (H + G) * dim + head * vdim;
+    const int p = tok_pos[m], slot = seq_slot[tok_seq[m]];
+    const int pidx = p / pg.page_size;
+    const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : 0;
+    const int pp = (page >= 0 && page < pg.n_pages) ? page : 0;       // page 0 is scratch
+    const size_t at = ((size_t)pp * G + head) * pg.page_size + p % pg.page_size;
+    bf16* cache = kind == 1 ? (bf16*)pg.k_pages + at * dim : kind == 2 ? (bf16*)pg.v_pages + at * vdim : nullptr;
+    const bool turns = cos_t && kind != 2;
+    const float* cs = turns ? cos_t + (size_t)min(p, max_pos - 1) * (rot >> 1) : nullptr;
+    const float* sn = turns ? sin_t + (size_t)min(p, max_pos - 1) * (rot >> 1) : nullptr;
+    const float* w = kind == 0 ? q_w : kind == 1 ? k_w : nullptr;
+    ti_pdl_sync();
+    qkv = ti_dependent(qkv);
+    bf16* row = qkv + (size_t)m * ld + off;
+    const float* b = bias ? bias + off : nullptr;
+    switch (n >> 5) {
+        case 2: head_prepare_lane<2>(row, b, w, eps, cs, sn, rot, pairing, cache, lane); break;
+        case 4: head_prepare_lane<4>(row, b, w, eps, cs, sn, rot, pairing, cache, lane); break;
+        default: head_prepare_lane<8>(row, b, w, eps, cs, sn, rot, pairing, cache, lane); break;
+    }
+}
+
 // A block takes GH virtual heads of one kv head and one map, and one range of the window's keys.
 // part_o [n_seq, virtual heads, splits, vdim], part_ml [n_seq, virtual heads, splits, 2] when splits > 1.
 template <typename T, typename OT, int GH, int VPL, int MODE>
@@ -743,6 +841,17 @@ extern "C" int ti_attn_head_prepare(void* qkv, long long ld, const float* bias, 
     const size_t smem = (size_t)warps * width * sizeof(float);
     TI_REQUIRE(smem <= 48 * 1024, "attn_head_prepare: heads of %d elements are not supported", width);
     const long long rows = (long long)M * (n_heads + 2 * n_kv_heads);
+    auto lanes = [](int n) { return n == 64 || n == 128 || n == 256; };
+    auto a16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    const int e_min = std::min(dim, vdim) / 32;
+    if (dtype == TI_BF16 && lanes(dim) && lanes(vdim) && ld % 8 == 0 && a16(qkv) && a16(k_pages) && a16(v_pages) &&
+        (!cos_t || pairing == 1 || (rot / 2) % (dim / 32) == 0) && e_min >= 2) {
+        TI_CUDA(ti_launch_class<2>(attn_head_prepare_vec_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, stream, (bf16*)qkv, ld, bias,
+                                   q_w, k_w, eps, cos_t, sin_t, cos_t ? rot : 0, pairing, max_pos, tok_pos, tok_seq, seq_slot, pg, rows, n_heads,
+                                   n_kv_heads, dim, vdim));
+        TI_CHECK_LAUNCH("attn_head_prepare (a lane a run)");
+        return 0;
+    }
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         TI_CUDA(ti_launch_class<2>(attn_head_prepare_kernel<T>, dim3((unsigned)((rows + warps - 1) / warps)), dim3(warps * 32), smem, stream,

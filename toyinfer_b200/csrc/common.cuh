@@ -165,6 +165,17 @@ __device__ __forceinline__ float ti_gate_act(float z, int kind) {
     return z / (1.0f + expf(-z));
 }
 
+// What a gated product stores for its (gate, up) pair.  kind 1 and 2: up * act(gate) as above; kind 3: a clamped gate
+// under a sharpened sigmoid, times the clamped up value plus one: g' = min(gate, limit), u' = clamp(up, -limit, limit),
+// g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float ti_gate_pair(float gate, float up, int kind, float limit) {
+    if (kind == 3) {
+        const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+        return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    }
+    return up * ti_gate_act(gate, kind);
+}
+
 template <typename F>
 static inline int ti_dispatch_dtype(int dtype, F&& f) {
     // f is called with a value of the element type

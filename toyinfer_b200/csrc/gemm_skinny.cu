@@ -47,6 +47,7 @@ struct Args {
     int M, N, K;
     long long ldx, ldw, ldo;
     int rows;       // weight rows per group, 8 to 16 (even for a gated product): see rows_per_group
+    float gate_limit = 0.f;     // the limit of a gated product of kind 3 (ti_gate_pair)
 };
 
 // NT: token tiles of 8 (1 or 2); WARPS per block; WPR: warps that share a group of 16 rows.
@@ -143,7 +144,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 16 ? 2 : 3) skinny_kernel
                     const int tok = n * 8 + 2 * t + (e & 1);
                     if (in_group + 1 < R && row + 1 < a.N && tok < a.M) {
                         const float gate = c[n][e], up = other[e];
-                        out[(size_t)tok * a.ldo + (size_t)(row >> 1)] = from_f32<OutT>(up * ti_gate_act(gate, GATED));
+                        out[(size_t)tok * a.ldo + (size_t)(row >> 1)] = from_f32<OutT>(ti_gate_pair(gate, up, GATED, a.gate_limit));
                     }
                 }
             }
@@ -194,6 +195,7 @@ int launch_wpr(const Args& a, int wpr, int sms, bool late_start, cudaStream_t st
 
 template <int NT>
 int launch_nt(const Args& a, int out_f32, int gated, int wpr, int sms, bool late_start, cudaStream_t stream) {
+    if (gated == 3) return launch_wpr<NT, 3, bf16>(a, wpr, sms, late_start, stream);
     if (gated == 2) return launch_wpr<NT, 2, bf16>(a, wpr, sms, late_start, stream);
     if (gated) return launch_wpr<NT, 1, bf16>(a, wpr, sms, late_start, stream);
     if (out_f32) return launch_wpr<NT, false, float>(a, wpr, sms, late_start, stream);
@@ -229,7 +231,7 @@ extern "C" void ti_set_skinny_rows(int rows) { g_force_rows = rows >= 8 && rows 
 // elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors.  `late_start`:
 // see the note on launching at the top of this file.
 extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                                long long ldw, long long ldo, int out_f32, int gated, int sms, int late_start,
+                                long long ldw, long long ldo, int out_f32, int gated, float gate_limit, int sms, int late_start,
                                 cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     TI_REQUIRE(M >= 1 && M <= 16 && N > 0 && K > 0, "linear (small batch): bad sizes M=%d N=%d K=%d", M, N, K);
@@ -248,6 +250,7 @@ extern "C" int ti_linear_skinny(const void* x, const void* w, void* out, int M, 
     while (wpr < 8 && steps >= (wpr * 2) * UNROLL) wpr *= 2;
     if (wpr == 8 && groups * 8 < target && steps >= 16 * UNROLL) wpr = 16;
     Args a{(const bf16*)x, (const bf16*)w, out, M, N, K, ldx, ldw, ldo, 16};
+    a.gate_limit = gate_limit;
     return M <= 8 ? launch_nt<1>(a, out_f32, gated, wpr, sms, late_start != 0, stream)
                   : launch_nt<2>(a, out_f32, gated, wpr, sms, late_start != 0, stream);
 }

@@ -239,13 +239,14 @@ extern "C" int ti_linear_tc_plan(int M, int N, int K, int sms, int* swap, int* b
 
 // x[M, K] (row stride ldx), w[N, K] (row stride ldw), both bfloat16; out[M, N] bfloat16 or
 // float32 with row stride ldo.  With `gated`, w's rows are (gate_0, up_0, gate_1, up_1, ...) and
-// out is [M, N / 2] = up * gate / (1 + exp(-gate)).  `workspace` (float32) and `tickets` (int32, zero before the
+// out is [M, N / 2] = up * gate / (1 + exp(-gate)) (gated 1; 2: the tanh form of gelu; 3: the clamped pair of
+// ti_gate_pair with `gate_limit`).  `workspace` (float32) and `tickets` (int32, zero before the
 // first use, left zero) as planned by ti_linear_tc_plan; tickets needs n_tiles entries and may be
 // null, in which case a second kernel adds the partial tiles of a split contraction, and the
 // many-token kernel deals out whole tiles only.
 extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                            long long ldw, long long ldo, int out_f32, int gated, int sms, float* workspace, int* tickets,
-                            cudaStream_t stream) {
+                            long long ldw, long long ldo, int out_f32, int gated, float gate_limit, int sms, float* workspace,
+                            int* tickets, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     TI_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     TI_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "linear (tcgen05): K and the row strides must be multiples of 8 elements");
@@ -258,7 +259,7 @@ extern "C" int ti_linear_tc(const void* x, const void* w, void* out, int M, int 
     g.rows_a = swap ? N : M; g.rows_b = swap ? M : N; g.K = K;
     g.out = out; g.ld_out = ldo; g.out_f32 = out_f32; g.transposed = swap;
     g.splits = splits; g.workspace = workspace; g.tickets = tickets;
-    g.gated = gated;
+    g.gated = gated; g.gate_limit = gate_limit;
     g.shared_tiles = p.walk && workspace && tickets ? p.shared : 0;      // without them: whole tiles only
     TI_REQUIRE(!gated || (N % 2 == 0 && !out_f32), "linear (tcgen05): a gated product needs an even number of weight rows and a bfloat16 result");
     CUtensorMap am, bm;

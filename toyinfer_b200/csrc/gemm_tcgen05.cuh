@@ -13,7 +13,8 @@ struct GemmArgs {
     int rows_a, rows_b, K;
     void* out; long long ld_out; int out_f32; int transposed;
     int splits; float* workspace; int* tickets;
-    int gated;      // rows of the weight operand come in (gate, up) pairs: store up * act(gate), half as many columns (1: silu, 2: gelu, tanh form)
+    int gated;      // rows of the weight operand come in (gate, up) pairs: store ti_gate_pair(gate, up), half as many columns (1: silu, 2: gelu, tanh form, 3: clamped)
+    float gate_limit;   // the limit of kind 3
     int shared_tiles;   // many-token kernel: the first so many tiles are shared out by contraction steps (see TileWalk)
 };
 
@@ -39,7 +40,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& g, int i, int b0, in
                 const int j = b0 + c + e;
                 if ((lane & 1) == 0 && i < g.rows_a && j < g.rows_b)
                     ((bf16*)g.out)[(size_t)j * g.ld_out + (i >> 1)] =
-                        __float2bfloat16_rn(other * ti_gate_act(mine, g.gated));
+                        __float2bfloat16_rn(ti_gate_pair(mine, other, g.gated, g.gate_limit));
             }
         } else if (i < g.rows_a) {
             const int j0 = b0 + c;
@@ -50,7 +51,7 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& g, int i, int b0, in
             for (int e = 0; e < 8; e++) {
                 const float gate = __bfloat162float(__float2bfloat16_rn(r[2 * e]));
                 const float up = __bfloat162float(__float2bfloat16_rn(r[2 * e + 1]));
-                z[e] = up * ti_gate_act(gate, g.gated);
+                z[e] = ti_gate_pair(gate, up, g.gated, g.gate_limit);
             }
             if (j0 + 16 <= g.rows_b && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll

@@ -51,7 +51,7 @@ __device__ __forceinline__ void fma_piece(float (&acc)[M], const uint4& wv, cons
 template <int M, int R, int U, int WPR, int GATED, typename OutT>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_kernel(const bf16* x, const bf16* __restrict__ w, OutT* __restrict__ out, int N, int K,
-            long long ldx, long long ldw, long long ldo) {
+            long long ldx, long long ldw, long long ldo, float gate_limit) {
     ti_pdl_trigger();
     __shared__ float part_sum[WPR > 1 ? WARPS * R * M : 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -116,7 +116,7 @@ gemv_kernel(const bf16* x, const bf16* __restrict__ w, OutT* __restrict__ out, i
 #pragma unroll
             for (int m = 0; m < M; m++) {
                 const float g = acc[r][m], up = acc[r + 1][m];
-                out[(size_t)m * ldo + (size_t)((row0 + r) >> 1)] = from_f32<OutT>(up * ti_gate_act(g, GATED));
+                out[(size_t)m * ldo + (size_t)((row0 + r) >> 1)] = from_f32<OutT>(ti_gate_pair(g, up, GATED, gate_limit));
             }
         }
     } else {
@@ -257,6 +257,7 @@ gemv_normed_kernel(const bf16* h, const bf16* delta, const NW* __restrict__ g, f
 
 struct Args {
     const bf16* x; const bf16* w; void* out; int N, K; long long ldx, ldw, ldo; cudaStream_t stream;
+    float gate_limit = 0.f;     // the limit of a gated product of kind 3 (ti_gate_pair)
 };
 
 template <int M, int R, int WPR, int GATED, typename OutT>
@@ -267,10 +268,10 @@ int launch(const Args& a, bool late_start) {
     TI_REQUIRE(blocks <= 0x7FFFFFFFll, "linear (few tokens): %d rows of weights are too many", a.N);
     if (late_start)
         TI_CUDA(ti_launch_after(gemv_kernel<M, R, U, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, a.stream, a.x, a.w,
-                                (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo));
+                                (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo, a.gate_limit));
     else
         TI_CUDA(ti_launch(gemv_kernel<M, R, U, WPR, GATED, OutT>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, a.stream, a.x, a.w,
-                          (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo));
+                          (OutT*)a.out, a.N, a.K, a.ldx, a.ldw, a.ldo, a.gate_limit));
     TI_CHECK_LAUNCH("linear (few tokens)");
     return 0;
 }
@@ -292,6 +293,7 @@ int launch_r(const Args& a, int rows, int wpr, bool late_start) {
 
 template <int M>
 int launch_m(const Args& a, int out_f32, int gated, int rows, int wpr, bool late_start) {
+    if (gated == 3) return launch_r<M, 3, bf16>(a, rows, wpr, late_start);
     if (gated == 2) return launch_r<M, 2, bf16>(a, rows, wpr, late_start);
     if (gated) return launch_r<M, 1, bf16>(a, rows, wpr, late_start);
     if (out_f32) return launch_r<M, false, float>(a, rows, wpr, late_start);
@@ -356,7 +358,7 @@ int launch_normed_r(const NormedArgs& a, int rows, int wpr) {
 // elements and the operands 16-byte aligned.  `sms`: the device's multiprocessors; the rows
 // per warp and the warps per row are chosen so that about 32 warps per SM have work.
 extern "C" int ti_linear_gemv(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
-                              long long ldw, long long ldo, int out_f32, int gated, int sms, int late_start,
+                              long long ldw, long long ldo, int out_f32, int gated, float gate_limit, int sms, int late_start,
                               cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     TI_REQUIRE(M >= 1 && M <= 2 && N > 0 && K > 0, "linear (few tokens): bad sizes M=%d N=%d K=%d", M, N, K);
@@ -367,6 +369,7 @@ extern "C" int ti_linear_gemv(const void* x, const void* w, void* out, int M, in
     int rows, wpr;
     choose_shape(M, N, K, sms, &rows, &wpr);
     Args a{(const bf16*)x, (const bf16*)w, out, N, K, ldx, ldw, ldo, stream};
+    a.gate_limit = gate_limit;
     return M == 1 ? launch_m<1>(a, out_f32, gated, rows, wpr, late_start != 0) : launch_m<2>(a, out_f32, gated, rows, wpr, late_start != 0);
 }
 

@@ -318,9 +318,9 @@ def linear_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, act: str = "silu", lim
     M, K = x.shape
     N = w_pairs.shape[0]
     ldx, ldw = _row_stride(x, "linear x"), _row_stride(w_pairs, "linear w")
-    if gemm.tc_eligible(x, w_pairs, K, ldx, ldw) and act in ("silu", "gelu_tanh"):
+    if gemm.tc_eligible(x, w_pairs, K, ldx, ldw):
         out = torch.empty((M, N // 2), dtype=x.dtype, device=x.device)
-        gemm.run(x, w_pairs, out, M, N, K, ldx, ldw, gated=1 + GATE_ACTS[act])      # the kernels' codes: 1 silu, 2 gelu
+        gemm.run(x, w_pairs, out, M, N, K, ldx, ldw, gated=1 + GATE_ACTS[act], gate_limit=limit)      # the kernels' codes: 1 silu, 2 gelu, 3 clamped
         return out
     return swiglu(linear(x, w_pairs), pairs=True) if act == "silu" else gated_act(linear(x, w_pairs), act, pairs=True, limit=limit)
 

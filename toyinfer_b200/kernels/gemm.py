@@ -76,20 +76,21 @@ def tc_eligible(x, w, K, ldx, ldw) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def run(x, w, out, M, N, K, ldx, ldw, gated: int = 0, late_start: bool = False) -> None:
-    """``gated``: 1 (or True) for up * silu(gate), 2 for up * gelu(gate) in the tanh form over paired weight rows; only for
-    shapes the tensor-core kernel takes (see tc_eligible).  ``late_start``: the
+def run(x, w, out, M, N, K, ldx, ldw, gated: int = 0, late_start: bool = False, gate_limit: float = 0.0) -> None:
+    """``gated``: 1 (or True) for up * silu(gate), 2 for up * gelu(gate) in the tanh form, 3 for the clamped pair
+    g' sigmoid(1.702 g') (u' + 1) with g' = min(gate, gate_limit), u' = clamp(up, -gate_limit, gate_limit), over paired
+    weight rows; only for shapes the tensor-core kernel takes (see tc_eligible).  ``late_start``: the
     few-token kernels start only when the kernel before them has finished (csrc/gemm_skinny.cu)."""
     lib = library()
     out_f32 = 1 if (out.dtype == torch.float32 and x.dtype != torch.float32) else 0
     if tc_eligible(x, w, K, ldx, ldw) and M <= GEMV_MAX_TOKENS:
         _call(lib.ti_linear_gemv, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, int(gated),
-              sm_count(x.device), 1 if late_start else 0, _stream())
+              float(gate_limit), sm_count(x.device), 1 if late_start else 0, _stream())
         return
     if tc_eligible(x, w, K, ldx, ldw) and (M <= SKINNY_MAX_TOKENS or (
             M <= SKINNY_SMALL_MAX_TOKENS and SKINNY_MAX_TOKENS >= 8 and K <= SKINNY_SMALL_MAX_K and N * K <= SKINNY_SMALL_MAX_WEIGHTS)):
         _call(lib.ti_linear_skinny, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, int(gated),
-              sm_count(x.device), 1 if late_start else 0, _stream())
+              float(gate_limit), sm_count(x.device), 1 if late_start else 0, _stream())
         return
     if tc_eligible(x, w, K, ldx, ldw):
         sms = sm_count(x.device)
@@ -110,8 +111,8 @@ def run(x, w, out, M, N, K, ldx, ldw, gated: int = 0, late_start: bool = False) 
             tickets = _tickets_for(x.device)
             if plan[1] > tickets.numel():
                 tickets = None
-        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, int(gated), sms,
-              _ptr(workspace), _ptr(tickets), _stream())
+        _call(lib.ti_linear_tc, _ptr(x), _ptr(w), _ptr(out), M, N, K, ldx, ldw, out.stride(0), out_f32, int(gated), float(gate_limit),
+              sms, _ptr(workspace), _ptr(tickets), _stream())
         return
     if gated:
         raise RuntimeError("linear: the gated epilogue exists in the tensor-core kernel only")

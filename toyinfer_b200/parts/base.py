@@ -13,7 +13,8 @@ Families and what each must provide:
 ``PositionEncoding`` either ``rotary_tables() -> (cos, sin, rot_dim)`` for the fused
                     rotate-and-store kernel, or ``apply(q, k, tok_pos)`` in place.
 ``Mixer``           ``memory_request()`` says what the cache must keep for it (keys
-                    and values, all or a window; a fixed-size state; nothing) and
+                    and values, all or a window; a fixed-size state; nothing; or a tuple
+                    of such requests, answered by a tuple of views in that order) and
                     ``forward(x, batch, mem, shared) -> y`` mixes ``x[M, hidden]``
                     along each sequence.  Sequence b of the step brings
                     ``batch.seq_new[b]`` tokens that follow ``batch.seq_start[b]``
