@@ -103,8 +103,19 @@ CASES = {
                                                _right(2, 64, 128, [0.9, 0.95]), 1.2, 0.7), "mlp": _moe(8, 2, 32, groups=(2, 1), scale=2.0, shared=48)},
         ],
     },
+    # sizes that are multiples of nothing: a width of 52 and a vocabulary of 97, heads of 10, 6, 5 and 3 elements, feed-forwards of
+    # 11 and 9; two streams
+    "T": {
+        "architecture": "Bolisun", "vocab": 97, "width": 52, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5}, "streams": 2,
+        "layers": [
+            {"type": "parallel", "mixer": _mix(_left(3, 1, 10, 6, 0.3, window=11, keep=2, rot={"base": 100.0, "dims": 6}),
+                                               _right(2, 5, 3, [0.9, 0.99]), 0.8, 0.5), "mlp": _dense(11, 2.0)},
+            {"type": "parallel", "mixer": _mix(_left(2, 2, 6, 10, 0.4, window=70, keep=65), _right(3, 3, 7, [0.95, 0.8, 0.999]), 1.0, 1.5),
+             "mlp": _moe(3, 2, 9, shared=7)},
+        ],
+    },
 }
-SEEDS = {"P": 35, "Q": 36, "R": 37, "S": 38}
+SEEDS = {"P": 35, "Q": 36, "R": 37, "S": 38, "T": 39}
 
 
 def case(name: str) -> dict:

@@ -452,83 +452,31 @@ __device__ __forceinline__ void load_run(const T* __restrict__ p, float (&x)[N],
     }
 }
 
-// The same for bfloat16 heads of 64, 128 or 256 elements on 16-byte-aligned rows: a lane holds E = n / 32 neighbouring
-// elements of the head in registers (one load of 4, 8 or 16 bytes, one store to the row and one to the cache), the sum of
-// squares is a warp's shuffle, a neighbour pair lies within a lane and a half pair in the lane rot / (2 E) further on.
-template <int E>
-__device__ __forceinline__ void head_prepare_lane(bf16* __restrict__ row, const float* __restrict__ bias, const float* __restrict__ w,
-                                                  float eps, const float* __restrict__ cs, const float* __restrict__ sn, int rot,
-                                                  int pairing, bf16* __restrict__ cache, int lane) {
-    constexpr int N = 32 * E;
-    const int i0 = lane * E;
-    float x[E];
-    load_run<bf16, E>(row + i0, x, true);
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; e++) {
-        if (bias) x[e] += bias[i0 + e];
-        ss = fmaf(x[e], x[e], ss);
-    }
-    if (w) {
-        const float inv = rsqrtf(warp_sum(ss) / (float)N + eps);
-#pragma unroll
-        for (int e = 0; e < E; e++) x[e] = x[e] * inv * w[i0 + e];
-    }
-    if (cs) {
-        const int half = rot >> 1;
-        if (pairing) {
-#pragma unroll
-            for (int e = 0; e < E; e += 2) {
-                if (i0 + e < rot) {
-                    const float c = cs[(i0 + e) >> 1], sv = sn[(i0 + e) >> 1], a = x[e], b = x[e + 1];
-                    x[e] = a * c - b * sv;
-                    x[e + 1] = b * c + a * sv;
-                }
-            }
-        } else {
-            const int hop = half / E;                   // lanes between the two elements of a pair (rot / 2 is a multiple of E)
-            const bool first = i0 < half;
-#pragma unroll
-            for (int e = 0; e < E; e++) {
-                const float o = __shfl_sync(0xffffffffu, x[e], first ? lane + hop : lane - hop);      // (lanes outside the rotation read anything)
-                if (i0 < rot) {
-                    const int f = first ? i0 + e : i0 + e - half;
-                    x[e] = first ? x[e] * cs[f] - o * sn[f] : x[e] * cs[f] + o * sn[f];
-                }
-            }
-        }
-    }
-    bf16 raw[E];
-#pragma unroll
-    for (int e = 0; e < E; e++) raw[e] = from_f32<bf16>(x[e]);
-    if constexpr (E == 8) {
-        *reinterpret_cast<uint4*>(row + i0) = *reinterpret_cast<const uint4*>(raw);
-        if (cache) *reinterpret_cast<uint4*>(cache + i0) = *reinterpret_cast<const uint4*>(raw);
-    } else if constexpr (E == 4) {
-        *reinterpret_cast<uint2*>(row + i0) = *reinterpret_cast<const uint2*>(raw);
-        if (cache) *reinterpret_cast<uint2*>(cache + i0) = *reinterpret_cast<const uint2*>(raw);
-    } else {
-        *reinterpret_cast<uint32_t*>(row + i0) = *reinterpret_cast<const uint32_t*>(raw);
-        if (cache) *reinterpret_cast<uint32_t*>(cache + i0) = *reinterpret_cast<const uint32_t*>(raw);
-    }
-}
-
+// The same for bfloat16 heads of 64, 128 or 256 elements on 16-byte-aligned rows: a lane holds 8 neighbouring elements of
+// a head in registers (one 16-byte load, one 16-byte store to the row and one to the cache), LANES = max(dim, vdim) / 8
+// lanes stand for a head (those past a shorter head's end idle) and a warp works on 32 / LANES heads at once; the sum of
+// squares is a shuffle among a head's lanes, a neighbour pair lies within a lane and a half pair rot / 16 lanes further on.
+template <int LANES>
 __global__ void attn_head_prepare_vec_kernel(bf16* __restrict__ qkv, long long ld, const float* __restrict__ bias,
                                              const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                              const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot, int pairing,
                                              int max_pos, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                              const int* __restrict__ seq_slot, Pages pg, long long rows, int H, int G, int dim, int vdim) {
     ti_pdl_trigger();
-    const int lane = threadIdx.x & 31;
-    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= rows) return;
+    constexpr int E = 8, RPW = 32 / LANES;
+    const int lane = threadIdx.x & 31, l = lane % LANES;
+    const long long r = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + lane / LANES;
+    const bool live = r < rows;
     const int per = H + 2 * G;
-    const long long m = r / per;
-    const int j = (int)(r - m * per);
+    const long long m = live ? r / per : 0;
+    const int j = live ? (int)(r - m * per) : 0;
     const int kind = j < H ? 0 : j < H + G ? 1 : 2;         // query, key, value
     const int head = kind == 0 ? j : kind == 1 ? j - H : j - H - G;
     const int n = kind == 2 ? vdim : dim;
     const int off = kind == 0 ? head * dim : kind == 1 ? H * dim + head * dim : (H + G) * dim + head * vdim;
+    const int i0 = l * E;
+    const bool mine = live && i0 < n;
+    // where the token's keys and values go does not depend on the kernel before this one
     const int p = tok_pos[m], slot = seq_slot[tok_seq[m]];
     const int pidx = p / pg.page_size;
     const int page = pidx < pg.table_width ? pg.page_table[(size_t)slot * pg.table_width + pidx] : 0;
@@ -536,17 +484,61 @@ __global__ void attn_head_prepare_vec_kernel(bf16* __restrict__ qkv, long long l
     const size_t at = ((size_t)pp * G + head) * pg.page_size + p % pg.page_size;
     bf16* cache = kind == 1 ? (bf16*)pg.k_pages + at * dim : kind == 2 ? (bf16*)pg.v_pages + at * vdim : nullptr;
     const bool turns = cos_t && kind != 2;
-    const float* cs = turns ? cos_t + (size_t)min(p, max_pos - 1) * (rot >> 1) : nullptr;
-    const float* sn = turns ? sin_t + (size_t)min(p, max_pos - 1) * (rot >> 1) : nullptr;
+    const int half = rot >> 1;
+    const float* cs = turns ? cos_t + (size_t)min(p, max_pos - 1) * half : nullptr;
+    const float* sn = turns ? sin_t + (size_t)min(p, max_pos - 1) * half : nullptr;
     const float* w = kind == 0 ? q_w : kind == 1 ? k_w : nullptr;
     ti_pdl_sync();
     qkv = ti_dependent(qkv);
     bf16* row = qkv + (size_t)m * ld + off;
-    const float* b = bias ? bias + off : nullptr;
-    switch (n >> 5) {
-        case 2: head_prepare_lane<2>(row, b, w, eps, cs, sn, rot, pairing, cache, lane); break;
-        case 4: head_prepare_lane<4>(row, b, w, eps, cs, sn, rot, pairing, cache, lane); break;
-        default: head_prepare_lane<8>(row, b, w, eps, cs, sn, rot, pairing, cache, lane); break;
+    float x[E];
+#pragma unroll
+    for (int e = 0; e < E; e++) x[e] = 0.f;
+    if (mine) load_run<bf16, E>(row + i0, x, true);
+    float ss = 0.f;
+    if (mine) {
+        if (bias) {
+            const float4 b0 = *reinterpret_cast<const float4*>(bias + off + i0), b1 = *reinterpret_cast<const float4*>(bias + off + i0 + 4);
+            x[0] += b0.x; x[1] += b0.y; x[2] += b0.z; x[3] += b0.w; x[4] += b1.x; x[5] += b1.y; x[6] += b1.z; x[7] += b1.w;
+        }
+#pragma unroll
+        for (int e = 0; e < E; e++) ss = fmaf(x[e], x[e], ss);
+    }
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);      // among a head's lanes
+    if (mine && w) {
+        const float inv = rsqrtf(ss / (float)n + eps);
+#pragma unroll
+        for (int e = 0; e < E; e++) x[e] = x[e] * inv * w[i0 + e];
+    }
+    if (cos_t) {                // (the same for the whole grid: every lane takes part in the exchange)
+        if (pairing) {
+            if (mine && turns) {
+#pragma unroll
+                for (int e = 0; e < E; e += 2) {
+                    if (i0 + e < rot) {
+                        const float c = cs[(i0 + e) >> 1], sv = sn[(i0 + e) >> 1], a = x[e], b = x[e + 1];
+                        x[e] = a * c - b * sv;
+                        x[e + 1] = b * c + a * sv;
+                    }
+                }
+            }
+        } else {
+            const int hop = half / E;                   // lanes between the two elements of a pair (rot / 2 is a multiple of 8)
+            const bool first = i0 < half;
+#pragma unroll
+            for (int e = 0; e < E; e++) {
+                const float o = __shfl_sync(0xffffffffu, x[e], first ? lane + hop : lane - hop);      // (lanes outside the rotation read anything)
+                if (mine && turns && i0 < rot) {
+                    const int f = first ? i0 + e : i0 + e - half;
+                    x[e] = first ? x[e] * cs[f] - o * sn[f] : x[e] * cs[f] + o * sn[f];
+                }
+            }
+        }
+    }
+    if (mine) {
+        store_run16<bf16, E>(row + i0, x);
+        if (cache) store_run16<bf16, E>(cache + i0, x);
     }
 }
 
@@ -843,12 +835,15 @@ extern "C" int ti_attn_head_prepare(void* qkv, long long ld, const float* bias, 
     const long long rows = (long long)M * (n_heads + 2 * n_kv_heads);
     auto lanes = [](int n) { return n == 64 || n == 128 || n == 256; };
     auto a16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    const int e_min = std::min(dim, vdim) / 32;
-    if (dtype == TI_BF16 && lanes(dim) && lanes(vdim) && ld % 8 == 0 && a16(qkv) && a16(k_pages) && a16(v_pages) &&
-        (!cos_t || pairing == 1 || (rot / 2) % (dim / 32) == 0) && e_min >= 2) {
-        TI_CUDA(ti_launch_class<2>(attn_head_prepare_vec_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, stream, (bf16*)qkv, ld, bias,
-                                   q_w, k_w, eps, cos_t, sin_t, cos_t ? rot : 0, pairing, max_pos, tok_pos, tok_seq, seq_slot, pg, rows, n_heads,
-                                   n_kv_heads, dim, vdim));
+    if (dtype == TI_BF16 && lanes(dim) && lanes(vdim) && ld % 8 == 0 && a16(qkv) && a16(k_pages) && a16(v_pages) && a16(bias) &&
+        (!cos_t || pairing == 1 || (rot / 2) % 8 == 0)) {
+        const int group = std::max(dim, vdim) / 8;          // lanes that stand for a head
+        const long long warps = (rows + 32 / group - 1) / (32 / group);
+        const dim3 grid((unsigned)((warps + 3) / 4)), block(128);
+#define TI_HEAD_PREPARE(L) TI_CUDA(ti_launch_class<2>(attn_head_prepare_vec_kernel<L>, grid, block, 0, stream, (bf16*)qkv, ld, bias, q_w, k_w, eps, \
+            cos_t, sin_t, cos_t ? rot : 0, pairing, max_pos, tok_pos, tok_seq, seq_slot, pg, rows, n_heads, n_kv_heads, dim, vdim))
+        if (group == 8) TI_HEAD_PREPARE(8); else if (group == 16) TI_HEAD_PREPARE(16); else TI_HEAD_PREPARE(32);
+#undef TI_HEAD_PREPARE
         TI_CHECK_LAUNCH("attn_head_prepare (a lane a run)");
         return 0;
     }
