@@ -14,6 +14,10 @@ with kept first positions and retention do) lets the pair run as ONE product in 
 The scales are applied to the members' 32-bit results before they are rounded, so the sum of the two scaled outputs is
 formed inside the output product's 32-bit accumulation.  Members that cannot say so run whole, one after the other, and
 a kernel forms the weighted sum.
+
+In a step of single tokens the two members' kernels are short and wait for one another for no reason: the second member
+then runs on a stream of its own between the two products (an event after the input product, an event before the output
+product; both are captured with the step when it is captured), so that a layer's chain is as long as the longer member's.
 """
 from __future__ import annotations
 
@@ -27,6 +31,8 @@ from .base import BuildContext, Mixer, ParamSpec, PartSpec, build_part, register
 
 
 class SideBySide(Mixer):
+    two_streams = True          # single-token steps run the second member beside the first (tests clear it to compare)
+
     def __init__(self, ctx: BuildContext, prefix: str, left: PartSpec, right: PartSpec, left_scale: float = 1.0,
                  right_scale: float = 1.0, names: Optional[Dict[str, str]] = None):
         n = {"left": "left.", "right": "right."}
@@ -39,6 +45,7 @@ class SideBySide(Mixer):
         self.joined = all(hasattr(m, "in_rows") and hasattr(m, "out_cols") and hasattr(m, "mix") for m in self.members)
         self.w_in = self.w_out = self.b_out = None
         self.pad = 0
+        self._side = None           # the second member's stream, made when first needed
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         out: Dict[str, ParamSpec] = {}
@@ -94,9 +101,23 @@ class SideBySide(Mixer):
             y = K.linear(x, self.w_in)
         M = y.shape[0]
         a = torch.empty((M, L.n_out + R.n_out), dtype=y.dtype, device=y.device)
+        y_right = y[:, L.n_in + self.pad:L.n_in + self.pad + R.n_in]
         with ranged(batch, "mixer.attention"):
-            L.mix(y[:, :L.n_in], batch, mem[0], out=a[:, :L.n_out], out_scale=self.scales[0])
-            R.mix(y[:, L.n_in + self.pad:L.n_in + self.pad + R.n_in], batch, mem[1], out=a[:, L.n_out:], out_scale=self.scales[1])
+            if self.two_streams and batch.mode == "extend" and y.is_cuda:
+                if self._side is None:
+                    self._side = torch.cuda.Stream(device=y.device)
+                main = torch.cuda.current_stream(y.device)
+                forked, joined = torch.cuda.Event(), torch.cuda.Event()
+                forked.record(main)
+                self._side.wait_event(forked)
+                with torch.cuda.stream(self._side):
+                    R.mix(y_right, batch, mem[1], out=a[:, L.n_out:], out_scale=self.scales[1])
+                    joined.record(self._side)
+                L.mix(y[:, :L.n_in], batch, mem[0], out=a[:, :L.n_out], out_scale=self.scales[0])
+                main.wait_event(joined)
+            else:
+                L.mix(y[:, :L.n_in], batch, mem[0], out=a[:, :L.n_out], out_scale=self.scales[0])
+                R.mix(y_right, batch, mem[1], out=a[:, L.n_out:], out_scale=self.scales[1])
         with ranged(batch, "mixer.out"):
             return K.linear_bias(a, self.w_out, self.b_out)
 
