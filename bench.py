@@ -520,11 +520,11 @@ def _bolisun_config(width, heads, layers, kind, vocab=32000):
                       "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
              "right": {"heads": max(1, heads // 2), "dim": 128, "vdim": 128,
                        "decay": [1.0 - 2.0 ** -(2 + 6 * h / max(1, heads // 2)) for h in range(max(1, heads // 2))]},
-             "left_scale": 0.8, "right_scale": 0.5}
+             "left_scale": 0.7, "right_scale": 0.6}
     if kind == "dense":
         mlp = {"kind": "dense", "ff": width * 8 // 3 // 128 * 128, "limit": 7.0}
     else:
-        mlp = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+        mlp = {"kind": "moe", "expert": {"ff": width // 2}, "router": {"experts": 16, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
                "shared": {"ff": width // 2}}
     layer = {"type": "parallel", "mixer": mixer, "mlp": mlp}
     return {"architecture": "Bolisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "streams": 4,

@@ -98,7 +98,7 @@ CASES = {
         "layers": [
             {"type": "parallel", "mixer": _mix(_left(4, 2, 128, 128, 0.09, window=96, keep=4,
                                                      rot={"base": 1e6, "dims": 64, "scaling": {"factor": 8.0, "original": 256, "fast": 16.0, "slow": 2.0}}),
-                                               _right(2, 128, 64, [0.97, 0.999]), 0.8, 0.5), "mlp": _dense(64, 2.0)},
+                                               _right(2, 128, 64, [0.97, 0.999]), 0.9, 0.4), "mlp": _dense(64, 2.0)},
             {"type": "parallel", "mixer": _mix(_left(4, 1, 64, 64, 0.125, window=80, keep=70, rot={"base": 1e4, "dims": 64}),
                                                _right(2, 64, 128, [0.9, 0.95]), 1.2, 0.7), "mlp": _moe(8, 2, 32, groups=(2, 1), scale=2.0, shared=48)},
         ],
@@ -109,7 +109,7 @@ CASES = {
         "architecture": "Bolisun", "vocab": 97, "width": 52, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.5}, "streams": 2,
         "layers": [
             {"type": "parallel", "mixer": _mix(_left(3, 1, 10, 6, 0.3, window=11, keep=2, rot={"base": 100.0, "dims": 6}),
-                                               _right(2, 5, 3, [0.9, 0.99]), 0.8, 0.5), "mlp": _dense(11, 2.0)},
+                                               _right(2, 5, 3, [0.9, 0.99]), 0.6, 0.75), "mlp": _dense(11, 2.0)},
             {"type": "parallel", "mixer": _mix(_left(2, 2, 6, 10, 0.4, window=70, keep=65), _right(3, 3, 7, [0.95, 0.8, 0.999]), 1.0, 1.5),
              "mlp": _moe(3, 2, 9, shared=7)},
         ],

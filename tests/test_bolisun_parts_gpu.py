@@ -362,7 +362,7 @@ def test_router_choices_against_the_rule():
     as less than nothing; equal scores (the lower index wins); all groups kept; no groups."""
     from toyinfer_b200.kernels import moe as KM
     g = torch.Generator().manual_seed(4)
-    for E, top, groups, keep, scale in [(6, 2, 3, 2, 1.5), (8, 4, 4, 2, 0.5), (16, 4, 4, 3, 2.5), (5, 3, 0, 0, 1.0), (4, 1, 2, 2, 1.0),
+    for E, top, groups, keep, scale in [(6, 2, 3, 2, 1.5), (8, 4, 4, 2, 0.5), (16, 3, 4, 3, 2.0), (5, 3, 0, 0, 1.0), (4, 1, 2, 2, 1.0),
                                         (12, 2, 6, 1, 3.0)]:
         M = 64
         z = torch.randn(M, E + 3, generator=g) * 2
