@@ -18,6 +18,7 @@ a kernel forms the weighted sum.
 In a step of single tokens the two members' kernels are short and wait for one another for no reason: the second member
 then runs on a stream of its own between the two products (an event after the input product, an event before the output
 product; both are captured with the step when it is captured), so that a layer's chain is as long as the longer member's.
+(In steps of many tokens the members' kernels fill the device one after the other; the same there gained nothing.)
 """
 from __future__ import annotations
 
