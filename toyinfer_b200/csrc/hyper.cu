@@ -90,7 +90,10 @@ extern "C" int ti_hyper_norm(float* X, const void* y, const float* gain, const f
     TI_REQUIRE(!(rows && write_back), "hyper_norm: gathered rows are not written back");
     const size_t smem = (size_t)(H + 33) * sizeof(float);
     TI_REQUIRE(smem <= 200 * 1024, "hyper_norm: rows of %d elements do not fit shared memory", H);
-    const int threads = H <= 256 ? 64 : H <= 1024 ? 128 : 256;
+    // few rows (a step of single tokens): a block is alone on its SM and its time is a thread's chain of loads, so a row's
+    // channels are spread over more threads
+    const int threads = R <= 296 ? (H <= 256 ? 64 : H <= 512 ? 128 : H <= 1024 ? 256 : H <= 2048 ? 512 : 1024)
+                                 : (H <= 256 ? 64 : H <= 1024 ? 128 : 256);
     return ti_dispatch_dtype(dtype, [&](auto t) -> int {
         using T = decltype(t);
         auto go = [&](auto sv) -> int {
